@@ -41,6 +41,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each request rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--max-seqs", type=int, default=4, help="state slots: the most requests live at any time")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
@@ -67,7 +68,7 @@ def main(argv=None) -> int:
         model = Model(build_spec(config), torch_dtype(args.dtype), args.device)
         model.load(random_tensors_as_loaded(model.weight_specs(), args.seed, torch_dtype(args.dtype), args.device))
     ecfg = EngineConfig(dtype=args.dtype, device=args.device, page_size=args.page_size,
-                        kv_cache_tokens=max(args.page_size, args.max_tokens), max_seqs=64)
+                        kv_cache_tokens=max(args.page_size, args.max_tokens), max_seqs=args.max_seqs)
     runner = StepRunner(model, ecfg)
     print("trace_run: ready", file=sys.stderr, flush=True)
 

@@ -204,3 +204,120 @@ def read_config_dict(folder_or_file: str) -> Dict[str, Any]:
     if not isinstance(d, dict):
         raise ConfigError(f"{path}: top level must be an object")
     return d
+
+
+def _require_number(d: Dict[str, Any], key: str, where: str = "config.json") -> float:
+    if key not in d:
+        raise ConfigError(f"{where}: required key '{key}' is missing")
+    v = d[key]
+    if isinstance(v, bool) or not isinstance(v, (int, float)):
+        raise ConfigError(f"{where}: '{key}' must be a number, got {v!r}")
+    return float(v)
+
+
+@dataclass(frozen=True)
+class KunonexLayer:
+    """One layer of a Kunonex model: which mixer it has, the mixer's sizes as
+    config.json gives them, and the width of its feed-forward (0 = none)."""
+
+    type: str = ""
+    mixer: Dict[str, Any] = field(default_factory=dict)
+    ff: int = 0
+    ff_kind: str = ""
+
+
+@dataclass(frozen=True)
+class KunonexConfig(ModelConfig):
+    """``Kunonex``: a decoder whose layers are listed one by one in config.json
+    (``layers``: ``type`` = ``mingru`` or ``latent_attention``, the mixer's
+    sizes under ``mixer``, the feed-forward under ``mlp`` or null), with a
+    stretch of layers (``loop``: ``start``, ``stop``, ``times``) that runs
+    several times in a row on the same weights.  Parallel blocks behind one
+    layer norm, token shift ahead of the mixer, sinusoidal positions added to
+    the embedding, PolyNorm feed-forwards."""
+
+    width: int = 0
+    vocab: int = 0
+    norm_eps: float = 1e-6
+    logit_scale: float = 1.0
+    layers: List[KunonexLayer] = field(default_factory=list)
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 0              # 0 = the model has no loop
+
+    ARCHITECTURE = "Kunonex"
+    MODEL_TYPE = "kunonex"
+    MIXERS = {"mingru": ("width",), "latent_attention": ("heads", "dim", "vdim", "kv_rank", "q_rank", "scale")}
+    FF_KINDS = ("dense",)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "KunonexConfig":
+        width = _require_int(d, "width")
+        vocab = _require_int(d, "vocab")
+        norm = d.get("norm")
+        if not isinstance(norm, dict):
+            raise ConfigError("config.json: 'norm' must be an object with 'eps'")
+        eps = _require_number(norm, "eps", "config.json norm")
+        raw_layers = d.get("layers")
+        if not isinstance(raw_layers, list) or not raw_layers:
+            raise ConfigError("config.json: 'layers' must be a non-empty list")
+        layers = []
+        for i, entry in enumerate(raw_layers):
+            where = f"config.json layers[{i}]"
+            if not isinstance(entry, dict):
+                raise ConfigError(f"{where}: must be an object")
+            kind = entry.get("type")
+            if kind not in cls.MIXERS:
+                raise ConfigError(f"{where}: type {kind!r} is not one of {sorted(cls.MIXERS)}")
+            mixer = entry.get("mixer")
+            if not isinstance(mixer, dict):
+                raise ConfigError(f"{where}: 'mixer' must be an object")
+            sizes = {}
+            for key in cls.MIXERS[kind]:
+                sizes[key] = _require_number(mixer, key, where) if key == "scale" else _require_int(mixer, key)
+            mlp = entry.get("mlp")
+            ff, ff_kind = 0, ""
+            if mlp is not None:
+                if not isinstance(mlp, dict):
+                    raise ConfigError(f"{where}: 'mlp' must be an object or null")
+                ff_kind = mlp.get("kind")
+                if ff_kind not in cls.FF_KINDS:
+                    raise ConfigError(f"{where}: mlp kind {ff_kind!r} is not one of {list(cls.FF_KINDS)}")
+                ff = _require_int(mlp, "ff")
+            layers.append(KunonexLayer(type=kind, mixer=sizes, ff=ff, ff_kind=ff_kind or ""))
+        start = stop = times = 0
+        loop = d.get("loop")
+        if loop is not None:
+            if not isinstance(loop, dict):
+                raise ConfigError("config.json: 'loop' must be an object or null")
+            start, stop = _require_int(loop, "start", 0), _require_int(loop, "stop", 0)
+            times = _require_int(loop, "times", 1)
+            if not 0 <= start < stop <= len(layers):
+                raise ConfigError(f"config.json: loop {start}..{stop} does not lie within the {len(layers)} layers")
+        arch = d.get("architecture") or (d.get("architectures") or [cls.ARCHITECTURE])[0]
+        cfg = cls(architectures=[str(arch)], model_type=str(d.get("model_type", "") or cls.MODEL_TYPE), width=width,
+                  vocab=vocab, norm_eps=eps, logit_scale=_opt_number(d, "logit_scale", 1.0), layers=layers,
+                  loop_start=start, loop_stop=stop, loop_times=times)
+        if cfg.norm_eps <= 0:
+            raise ConfigError(f"norm eps must be positive, got {cfg.norm_eps}")
+        return cfg
+
+    # what Engine and the command line read of any model's configuration
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @property
+    def eos_token_id(self) -> Optional[int]:
+        return None
+
+    def to_dict(self) -> Dict[str, Any]:
+        """The config.json this configuration was read from (its own keys)."""
+        out: Dict[str, Any] = {
+            "architecture": self.architecture, "width": self.width, "vocab": self.vocab,
+            "norm": {"eps": self.norm_eps}, "logit_scale": self.logit_scale,
+            "layers": [{"type": l.type, "mixer": dict(l.mixer),
+                        "mlp": {"kind": l.ff_kind, "ff": l.ff} if l.ff else None} for l in self.layers]}
+        if self.loop_times:
+            out["loop"] = {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times}
+        return out

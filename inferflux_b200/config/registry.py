@@ -18,7 +18,7 @@ _ARCHITECTURES: Dict[str, Tuple[Type[ModelConfig], Callable[[Any], ModelSpec]]] 
 _ALIASES: Dict[str, str] = {}
 
 PART_FAMILIES = ("mixer", "feed_forward", "norm", "position", "arrangement",
-                 "embedding", "lm_head")
+                 "embedding", "lm_head", "shift", "junction")
 _PARTS: Dict[str, Dict[str, type]] = {fam: {} for fam in PART_FAMILIES}
 
 
@@ -32,7 +32,9 @@ def register_architecture(name: str, config_cls: Type[ModelConfig],
 
 def resolve_architecture(config_dict: Dict[str, Any]) -> str:
     _ensure_builtin()
-    archs = config_dict.get("architectures") or []
+    archs = list(config_dict.get("architectures") or [])
+    if isinstance(config_dict.get("architecture"), str):      # some configurations name theirs in the singular
+        archs.append(config_dict["architecture"])
     for a in archs:
         if a in _ARCHITECTURES:
             return a

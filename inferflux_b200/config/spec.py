@@ -63,11 +63,14 @@ class Run:
     ``layer`` indexes :attr:`ModelSpec.layers`; a layer may appear in several
     runs (its weights are shared, each run has a cache of its own).
     ``cache_of`` names an earlier run whose cache this run reads instead of
-    writing one of its own.
+    writing one of its own.  ``params`` is what distinguishes this run from
+    the layer's other runs for the parts that ask (the number of the pass in a
+    loop over the same layers, say); parts find it in ``RunInfo.params``.
     """
 
     layer: int
     cache_of: Optional[int] = None
+    params: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass

@@ -1,0 +1,267 @@
+// Latent attention: a token caches one latent vector c (rank R) from which every head's keys and values
+// follow, k_h = Uk_h c and v_h = Uv_h c.  The products are moved to the query's side,
+//
+//   score_h(i, j) = q_h(i) . (Uk_h c_j) = (Uk_h^T q_h(i)) . c_j            o_h(i) = Uv_h (sum_j p_h(i, j) c_j)
+//
+// so the kernel attends over the cached latents alone: its queries are the R-wide vectors Uk_h^T q_h, its keys
+// and its values are both c, and its output is the R-wide weighted sum that the caller sends through Uv_h.
+// Scores, softmax and sums are float32 (expf, running maximum and sum); causal: key j is visible to the query
+// at position p iff j <= p.  No positions enter.
+//
+// latent_prep turns a token's stacked down projections into what the step needs: the query latent and the
+// key/value latent each divided by their root mean square and multiplied by their weights (the key/value
+// latent goes straight to the token's place in the paged cache), and the sigmoid of the per-head output gates.
+//
+// attn_latent_paged: one block takes 16 consecutive new tokens of one request and one head and walks the
+// request's pages in tiles of 32 latents that serve as keys and as values.  Tiles start at multiples of 32 and
+// are added in index order, so a token's result does not depend on how the prompt was cut.
+#include "common.cuh"
+
+namespace {
+constexpr int LQ = 16;        // query rows per block (2 per warp, 8 warps)
+constexpr int LKEYS = 32;     // latents per tile (one per lane)
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+template <typename T>
+__global__ void latent_prep_kernel(const float* __restrict__ p, long long p_stride, const float* __restrict__ wq,
+                                   const float* __restrict__ wkv, float eps, int q_rank, int kv_rank, int n_heads,
+                                   T* __restrict__ cq, T* __restrict__ cache, long long page_stride, int page_size,
+                                   const int* __restrict__ slot_map, float* __restrict__ gate) {
+  pdl_enter();
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const float* pr = p + (size_t)row * p_stride;
+  float sq = 0.0f;
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) sq = fmaf(pr[i], pr[i], sq);
+  const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)q_rank + eps);
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+    cq[(size_t)row * q_rank + i] = Num<T>::from_f(pr[i] * rq * wq[i]);
+  const float* pk = pr + q_rank;
+  sq = 0.0f;
+  for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) sq = fmaf(pk[i], pk[i], sq);
+  const float rk = 1.0f / sqrtf(block_sum(sq, red) / (float)kv_rank + eps);
+  const int slot = slot_map[row];
+  if (slot >= 0) {
+    T* c = cache + (size_t)(slot / page_size) * page_stride + (size_t)(slot % page_size) * kv_rank;
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) c[i] = Num<T>::from_f(pk[i] * rk * wkv[i]);
+  }
+  const float* pg = pk + kv_rank;
+  for (int i = threadIdx.x; i < n_heads; i += blockDim.x) gate[(size_t)row * n_heads + i] = sigmoid_f(pg[i]);
+}
+
+struct LatentBatch {
+  const int* block_tables;    // [n_entries, bt_stride] page of each logical block, -1 = given back
+  int bt_stride;
+  const int* tile_entry;      // [n_tiles] request entry of each query tile
+  const int* tile_q0;         // [n_tiles] first new token (within the entry) of the tile
+  const int* entry_q_start;   // [n_entries] row of the entry's first new token in q/out
+  const int* entry_q_len;     // [n_entries] new tokens
+  const int* entry_ctx_start; // [n_entries] tokens cached before them = position of the first new token
+};
+
+// Where a (token, head) vector of `rank` elements lies: token * row + head * head elements from the start.
+struct HeadLayout { long long row, head; };
+
+// q float32, out of the cache's type T, each laid out by its HeadLayout.  cache: the run's latents of page 0,
+// [slot][rank] within a page.
+template <typename T, int NACC>
+__global__ void __launch_bounds__(256)
+attn_latent_paged_kernel(const float* __restrict__ q, HeadLayout ql, T* __restrict__ out, HeadLayout ol,
+                         const T* __restrict__ cache, long long page_stride, int page_size, int page_shift,
+                         LatentBatch b, int rank, float scale) {
+  pdl_enter();
+  extern __shared__ float smem[];
+  float* qs = smem;                               // [LQ][rank]
+  float* cs = qs + LQ * rank;                     // [LKEYS][rank + 1]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int e = b.tile_entry[tile];
+  const int q0 = b.tile_q0[tile];
+  const int rows = min(LQ, b.entry_q_len[e] - q0);
+  if (rows <= 0) return;
+  const int tok0 = b.entry_q_start[e] + q0;
+  const int pos0 = b.entry_ctx_start[e] + q0;
+  const int* bt = b.block_tables + (size_t)e * b.bt_stride;
+
+  for (int idx = tid; idx < LQ * rank; idx += blockDim.x) {
+    const int r = idx / rank, d = idx - r * rank;
+    qs[idx] = r < rows ? q[(size_t)(tok0 + r) * ql.row + (size_t)head * ql.head + d] : 0.0f;
+  }
+
+  const int r0 = warp * 2, r1 = r0 + 1;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+  float o[2][NACC];
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) { o[0][a] = 0.0f; o[1][a] = 0.0f; }
+
+  const int kend = pos0 + rows - 1;               // last key any row of the tile may see
+  for (int k0 = 0; k0 <= kend; k0 += LKEYS) {
+    __syncthreads();
+    for (int idx = tid; idx < LKEYS * rank; idx += blockDim.x) {
+      const int j = idx / rank, d = idx - j * rank;
+      const int key = k0 + j;
+      float c = 0.0f;
+      if (key <= kend) {
+        const int page = bt[key >> page_shift];
+        if (page >= 0) c = Num<T>::to_f(cache[(size_t)page * page_stride + (size_t)(key & (page_size - 1)) * rank + d]);
+      }
+      cs[j * (rank + 1) + d] = c;
+    }
+    __syncthreads();
+    if (r0 < rows) {                               // warp-uniform
+      const bool two = r1 < rows;
+      const float* cr = cs + lane * (rank + 1);
+      const float* qa = qs + r0 * rank;
+      const float* qb = qs + r1 * rank;
+      float s0 = 0.0f, s1 = 0.0f;
+      for (int d = 0; d < rank; ++d) {
+        const float cd = cr[d];
+        s0 = fmaf(qa[d], cd, s0);
+        s1 = fmaf(qb[d], cd, s1);
+      }
+      const int key = k0 + lane;
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        if (rr == 1 && !two) break;
+        const int p = pos0 + r0 + rr;
+        const bool visible = key <= p;
+        const float s = visible ? (rr ? s1 : s0) * scale : -INFINITY;
+        const float m_new = fmaxf(m[rr], warp_max(s));
+        if (m_new == -INFINITY) continue;          // nothing visible to this row yet (warp-uniform)
+        const float alpha = expf(m[rr] - m_new);   // exp(-inf) = 0 on the first visible tile
+        const float pj = visible ? expf(s - m_new) : 0.0f;
+        l[rr] = l[rr] * alpha + warp_sum(pj);
+        m[rr] = m_new;
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) o[rr][a] *= alpha;
+        for (int j = 0; j < LKEYS; ++j) {
+          const float pjj = __shfl_sync(0xffffffffu, pj, j);
+          if (pjj == 0.0f) continue;               // warp-uniform; also keeps stale latents out
+#pragma unroll
+          for (int a = 0; a < NACC; ++a) {
+            const int d = lane + 32 * a;
+            if (d < rank) o[rr][a] = fmaf(pjj, cs[j * (rank + 1) + d], o[rr][a]);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const int r = r0 + rr;
+    if (r >= rows) continue;
+    const float inv = l[rr] > 0.0f ? 1.0f / l[rr] : 0.0f;
+    T* orow = out + (size_t)(tok0 + r) * ol.row + (size_t)head * ol.head;
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) {
+      const int d = lane + 32 * a;
+      if (d < rank) orow[d] = Num<T>::from_f(o[rr][a] * inv);
+    }
+  }
+}
+
+template <typename T, int NACC>
+int launch_latent(const float* q, HeadLayout ql, void* out, HeadLayout ol, const void* cache, long long page_stride,
+                  int page_size, LatentBatch b, int n_tiles, int n_heads, int rank, float scale, cudaStream_t stream) {
+  const size_t smem = ((size_t)LQ * rank + (size_t)LKEYS * (rank + 1)) * sizeof(float);
+  auto kern = attn_latent_paged_kernel<T, NACC>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  const int rc = launch_pdl(kern, dim3(n_tiles, n_heads), dim3(256), smem, stream, q, ql, (T*)out, ol, (const T*)cache,
+                            page_stride, page_size, page_shift, b, rank, scale);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
+template <typename T>
+int dispatch_latent(const float* q, HeadLayout ql, void* out, HeadLayout ol, const void* cache, long long page_stride,
+                    int page_size, LatentBatch b, int n_tiles, int n_heads, int rank, float scale, cudaStream_t stream) {
+  const int nacc = (rank + 31) / 32;
+#define IFX_LAT(N) return launch_latent<T, N>(q, ql, out, ol, cache, page_stride, page_size, b, n_tiles, n_heads, rank, scale, stream)
+  if (nacc <= 1) IFX_LAT(1);
+  if (nacc <= 2) IFX_LAT(2);
+  if (nacc <= 4) IFX_LAT(4);
+  if (nacc <= 8) IFX_LAT(8);
+  if (nacc <= 16) IFX_LAT(16);
+  IFX_LAT(32);
+#undef IFX_LAT
+}
+}  // namespace
+
+// p float32 [N, q_rank + kv_rank + n_heads] (row stride p_stride): a token's down projections side by side.
+// cq [N, q_rank] and the cache are of dtype; gate float32 [N, n_heads]; slot_map [N] = page * page_size +
+// place within the page of each token's latent (-1: not written).
+IFX_API int ifx_latent_prep(const float* p, long long p_stride, const float* wq, const float* wkv, float eps, int q_rank,
+                            int kv_rank, int n_heads, void* cq, void* cache, int dtype, long long page_stride,
+                            int page_size, const int* slot_map, float* gate, int n_rows, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (q_rank < 1 || kv_rank < 1 || n_heads < 1 || page_size < 1) return IFX_ERR_UNSUPPORTED;
+  const int widest = q_rank > kv_rank ? q_rank : kv_rank;
+  int threads = 64;
+  while (threads < 1024 && threads * 4 < widest) threads <<= 1;
+  int rc;
+  if (dtype == IFX_F32)
+    rc = launch_pdl(latent_prep_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, p, p_stride, wq, wkv, eps, q_rank,
+                    kv_rank, n_heads, (float*)cq, (float*)cache, page_stride, page_size, slot_map, gate);
+  else if (dtype == IFX_BF16)
+    rc = launch_pdl(latent_prep_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, p, p_stride, wq, wkv, eps, q_rank,
+                    kv_rank, n_heads, (bf16*)cq, (bf16*)cache, page_stride, page_size, slot_map, gate);
+  else
+    return IFX_ERR_UNSUPPORTED;
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
+namespace {
+// out[t, h, :] = in[t, h, :] * gate[t, h], from float32 rows laid out by `il` into contiguous [N, heads * width]
+// rows of the engine's type: the per-head output gate, the rounding and the gathering of the heads in one pass.
+template <typename TO>
+__global__ void gate_heads_kernel(const float* __restrict__ in, HeadLayout il, const float* __restrict__ gate,
+                                  TO* __restrict__ out, int n_heads, int width) {
+  pdl_enter();
+  const int row = blockIdx.x;
+  const int total = n_heads * width;
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int h = i / width, d = i - h * width;
+    out[(size_t)row * total + i] = Num<TO>::from_f(in[(size_t)row * il.row + (size_t)h * il.head + d] * gate[(size_t)row * n_heads + h]);
+  }
+}
+}  // namespace
+
+IFX_API int ifx_gate_heads(const float* in, long long in_row, long long in_head, const float* gate, void* out, int out_dtype,
+                           int n_rows, int n_heads, int width, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const int total = n_heads * width;
+  const int threads = total >= 1024 ? 256 : (total >= 256 ? 128 : 64);
+  HeadLayout il{in_row, in_head};
+  int rc;
+  if (out_dtype == IFX_F32)
+    rc = launch_pdl(gate_heads_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, in, il, gate, (float*)out, n_heads, width);
+  else if (out_dtype == IFX_BF16)
+    rc = launch_pdl(gate_heads_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, in, il, gate, (bf16*)out, n_heads, width);
+  else
+    return IFX_ERR_UNSUPPORTED;
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
+// Query tiles are 16 tokens of one entry: tile_entry / tile_q0 list them.  rank: 1..1024.  q float32 and out (of
+// the cache's type) hold a (token, head) vector at token * row + head * head elements.
+IFX_API int ifx_attn_latent_paged(const float* q, long long q_row, long long q_head, void* out, long long o_row,
+                                  long long o_head, const void* cache, int cache_dtype, long long page_stride,
+                                  int page_size, const int* block_tables, int bt_stride, const int* tile_entry,
+                                  const int* tile_q0, int n_tiles, const int* entry_q_start, const int* entry_q_len,
+                                  const int* entry_ctx_start, int n_heads, int rank, float scale, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (rank < 1 || rank > 1024 || n_heads < 1 || n_heads > 65535) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
+  LatentBatch b{block_tables, bt_stride, tile_entry, tile_q0, entry_q_start, entry_q_len, entry_ctx_start};
+  HeadLayout ql{q_row, q_head}, ol{o_row, o_head};
+  if (cache_dtype == IFX_F32)
+    return dispatch_latent<float>(q, ql, out, ol, cache, page_stride, page_size, b, n_tiles, n_heads, rank, scale, stream);
+  if (cache_dtype == IFX_BF16)
+    return dispatch_latent<bf16>(q, ql, out, ol, cache, page_stride, page_size, b, n_tiles, n_heads, rank, scale, stream);
+  return IFX_ERR_UNSUPPORTED;
+}

@@ -1,0 +1,63 @@
+// PolyNorm activation of a feed-forward:  y = a N(z) + b N(z^2) + c N(z^3) + e  with powers taken element by
+// element and N(v) = v / sqrt(mean(v^2) + eps) over a token's row; z = the up projection's float32 sums plus
+// its bias.  One block per row; the row stays in shared memory between the sums and the output.  The three
+// mean squares and the result are float32; the output is rounded once to the engine's type.
+#include "common.cuh"
+
+namespace {
+template <typename TO>
+__global__ void polynorm_kernel(const float* __restrict__ z, long long z_stride, const float* __restrict__ bias,
+                                const float* __restrict__ coeff, float eps, TO* __restrict__ out, int n) {
+  pdl_enter();
+  extern __shared__ float row_buf[];
+  __shared__ float red[32];
+  const float* zr = z + (size_t)blockIdx.x * z_stride;
+  float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = zr[i] + (bias ? bias[i] : 0.0f);
+    row_buf[i] = v;
+    const float v2 = v * v, v3 = v2 * v;
+    s1 = fmaf(v, v, s1);
+    s2 = fmaf(v2, v2, s2);
+    s3 = fmaf(v3, v3, s3);
+  }
+  s1 = block_sum(s1, red);
+  s2 = block_sum(s2, red);
+  s3 = block_sum(s3, red);
+  const float r1 = coeff[0] / sqrtf(s1 / (float)n + eps);
+  const float r2 = coeff[1] / sqrtf(s2 / (float)n + eps);
+  const float r3 = coeff[2] / sqrtf(s3 / (float)n + eps);
+  const float e = coeff[3];
+  TO* o = out + (size_t)blockIdx.x * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = row_buf[i];
+    const float v2 = v * v;
+    o[i] = Num<TO>::from_f(fmaf(v, r1, fmaf(v2, r2, fmaf(v2 * v, r3, e))));
+  }
+}
+}  // namespace
+
+// z float32 [rows, n] (row stride z_stride), bias float32 [n] or null, coeff float32 [4] = a, b, c, e.
+IFX_API int ifx_polynorm(const float* z, long long z_stride, const float* bias, const float* coeff, float eps, void* out,
+                         int out_dtype, int n_rows, int n, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const size_t smem = (size_t)n * sizeof(float);
+  if (smem > 200 * 1024) return IFX_ERR_UNSUPPORTED;
+  int threads = 64;
+  while (threads < 1024 && threads * 4 < n) threads <<= 1;
+  int rc;
+  if (out_dtype == IFX_F32) {
+    auto kern = polynorm_kernel<float>;
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return (int)cudaGetLastError();
+    rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, z, z_stride, bias, coeff, eps, (float*)out, n);
+  } else if (out_dtype == IFX_BF16) {
+    auto kern = polynorm_kernel<bf16>;
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return (int)cudaGetLastError();
+    rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, z, z_stride, bias, coeff, eps, (bf16*)out, n);
+  } else {
+    return IFX_ERR_UNSUPPORTED;
+  }
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}

@@ -130,6 +130,8 @@ class StepContext:
     device: str
     position_tables: Dict[str, object] = field(default_factory=dict)   # position name -> what its prepare() returned
     extras: Dict[str, object] = field(default_factory=dict)            # describe_key -> what describe_step() returned
+    embedding_output: object = None           # float32 [N, hidden]: the stream before the first layer, kept when a block asks
+    scratch: Dict[object, object] = field(default_factory=dict)        # what a part computes once per step for all its runs
 
     def buffer(self, shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

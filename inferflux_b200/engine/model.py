@@ -40,6 +40,7 @@ class Model:
             self.blocks.append(arrangement(parts, layer.position))
         self._plan_cache()
         self._describers = self._collect_describers()
+        self._keeps_embedding = any(getattr(b, "needs_embedding_output", False) for b in self.blocks)
 
     @staticmethod
     def _roles(layer) -> Dict[str, str]:
@@ -98,7 +99,7 @@ class Model:
                 states += list(cls.state_needs(ps.params))
             if len({s.name for s in states}) != len(states):
                 raise ValueError(f"layer {run.layer}: two state tensors of its parts have the same name")
-            info = RunInfo(run_index=i)
+            info = RunInfo(run_index=i, params=dict(run.params))
             if run.cache_of is not None:
                 if need is not None:
                     raise ValueError(f"schedule[{i}]: layer {run.layer} writes keys and values of its own "
@@ -161,9 +162,12 @@ class Model:
     # ------------------------------------------------------------------- step
     def forward(self, ctx) -> torch.Tensor:
         """Run the step's tokens through every run; float32 logits [n_want, vocab]."""
+        ctx.scratch.clear()            # a context may be run twice (once eagerly, once while a graph is recorded)
         for name, pos in self.positions.items():
             ctx.position_tables[name] = pos.prepare(ctx)
-        residual = self.embedding.forward(ctx.token_ids)
+        residual = self.embedding.forward_step(ctx)
+        if self._keeps_embedding:
+            ctx.embedding_output = residual.clone()      # a block reads the stream as the embedding left it
         delta = None
         for info in self.runs:
             delta = self.blocks[self.spec.schedule[info.run_index].layer].forward(residual, delta, ctx, info)

@@ -106,6 +106,31 @@ def _lib():
                      "ifx_attn_prefill_bf16", "ifx_attn_decode_bf16", "ifx_gemv_bf16", "ifx_attn_prefill_umma",
                      "ifx_apply_penalties", "ifx_sample"):
             getattr(lib, name).restype = c_int
+        c_double = ctypes.c_double
+        lib.ifx_add_layernorm.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p, c_float, c_void_p, c_int,
+                                          c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_add_layernorm_shift1.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p, c_float, c_void_p,
+                                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_token_shift.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_int, c_int, c_int, c_void_p]
+        lib.ifx_embed_sinusoid_layernorm.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_double,
+                                                     c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_polynorm.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_mingru_segment.argtypes = []
+        lib.ifx_mingru_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+        lib.ifx_latent_prep.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p,
+                                        c_void_p, c_int, c_ll, c_int, c_void_p, c_void_p, c_int, c_void_p]
+        lib.ifx_attn_latent_paged.argtypes = [c_void_p, c_ll, c_ll, c_void_p, c_ll, c_ll, c_void_p, c_int, c_ll, c_int,
+                                              c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                              c_int, c_int, c_float, c_void_p]
+        lib.ifx_add_into.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_void_p]
+        lib.ifx_add_rows_vector.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.ifx_gate_heads.argtypes = [c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        for name in ("ifx_add_layernorm", "ifx_add_layernorm_shift1", "ifx_token_shift", "ifx_embed_sinusoid_layernorm",
+                     "ifx_polynorm", "ifx_mingru_segment", "ifx_mingru_scan", "ifx_latent_prep", "ifx_attn_latent_paged", "ifx_gate_heads",
+                     "ifx_add_into", "ifx_add_rows_vector"):
+            getattr(lib, name).restype = c_int
         _sigs_done = True
     return lib
 
@@ -781,4 +806,228 @@ def sample(logits: torch.Tensor, weights: torch.Tensor, temperature: torch.Tenso
     _check(_lib().ifx_sample(_ptr(logits), logits.stride(0), _ptr(weights), _ptr(temperature), _ptr(top_k),
                              _ptr(top_p), _ptr(min_p), _ptr(seeds), _ptr(counters), _ptr(out), r, v, _stream()),
            "sample")
+    return out
+
+
+# ------------------------------------- layer norm, token shift, sinusoidal embedding, PolyNorm, minGRU, latent attention
+def add_layernorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                  out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None, n_partials: int = 1,
+                  out32: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """residual (float32 [N, H]) += delta; out = (r - mean) / sqrt(var + eps) * weight.
+
+    The arguments are those of :func:`add_rmsnorm`; ``out32`` (float32
+    ``[rows, H]``) takes the normed rows unrounded beside ``out``."""
+    n, hidden = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_layernorm: residual float32 contiguous")
+    _need(weight.dtype == torch.float32 and weight.numel() == hidden, "add_layernorm: weight float32 [H]")
+    n_rows = rows.numel() if rows is not None else n
+    if rows is not None:
+        _need(rows.dtype == torch.int32, "add_layernorm: rows int32")
+    pstride = 0
+    if delta is not None:
+        _need(delta.is_contiguous(), "add_layernorm: delta contiguous")
+        if n_partials > 1:
+            _need(tuple(delta.shape) == (n_partials, n, hidden), "add_layernorm: partials [P, N, H]")
+            pstride = n * hidden
+        else:
+            _need(tuple(delta.shape)[-2:] == (n, hidden) and delta.numel() == n * hidden, "add_layernorm: delta [N, H]")
+    for o in (out, out32):
+        if o is not None:
+            _need(o.is_contiguous() and tuple(o.shape) == (n_rows, hidden), "add_layernorm: out [rows, H]")
+    if out32 is not None:
+        _need(out32.dtype == torch.float32, "add_layernorm: out32 float32")
+    dd = _code(delta) if delta is not None else F32
+    od = _code(out) if out is not None else F32
+    _check(_lib().ifx_add_layernorm(_ptr(residual), _ptr(delta), dd, n_partials, pstride, _ptr(weight), float(eps),
+                                    _ptr(out), od, _ptr(out32), _ptr(rows), n_rows, hidden,
+                                    0 if rows is not None else 1, _stream()), "add_layernorm")
+    return out
+
+
+def add_layernorm_shift1(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                         mu: torch.Tensor, state: torch.Tensor, entry_slot: torch.Tensor, out: torch.Tensor,
+                         shifted: torch.Tensor, n_partials: int = 1) -> None:
+    """A step of single tokens (row t is entry t): residual sum, layer norm,
+    ``shifted = h + (state[slot] - h) * mu`` and ``state[slot] = h`` in one
+    kernel.  state float32 [slots, H]."""
+    n, hidden = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_layernorm_shift1: residual float32 contiguous")
+    _need(weight.dtype == torch.float32 and mu.dtype == torch.float32 and weight.numel() == hidden
+          and mu.numel() == hidden, "add_layernorm_shift1: weight and mu float32 [H]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == hidden,
+          "add_layernorm_shift1: state float32 [slots, H]")
+    _need(entry_slot.dtype == torch.int32 and entry_slot.numel() >= n, "add_layernorm_shift1: one slot per row")
+    pstride = 0
+    if delta is not None:
+        _need(delta.is_contiguous() and delta.numel() == n_partials * n * hidden, "add_layernorm_shift1: delta [P, N, H]")
+        pstride = n * hidden if n_partials > 1 else 0
+    for o in (out, shifted):
+        _need(o.is_contiguous() and tuple(o.shape) == (n, hidden) and o.dtype == out.dtype, "add_layernorm_shift1: out [N, H]")
+    _check(_lib().ifx_add_layernorm_shift1(_ptr(residual), _ptr(delta), _code(delta) if delta is not None else F32,
+                                           n_partials, pstride, _ptr(weight), float(eps), _ptr(mu), _ptr(state),
+                                           _ptr(entry_slot), _ptr(out), _ptr(shifted), _code(out), n, hidden, _stream()),
+           "add_layernorm_shift1")
+
+
+def token_shift(h32: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, row_entry: torch.Tensor,
+                entry_q_start: torch.Tensor, entry_q_len: torch.Tensor, entry_slot: torch.Tensor,
+                out: torch.Tensor) -> torch.Tensor:
+    """out[t] = h32[t] + (before(t) - h32[t]) * mu, where before(t) is the row
+    above within the same entry or, for an entry's first row, what its state
+    slot holds; the slot then takes the entry's last row.  h32 float32 [N, H],
+    state float32 [slots, H], row_entry int32 [N]."""
+    n, hidden = h32.shape
+    _need(h32.dtype == torch.float32 and h32.is_contiguous(), "token_shift: h32 float32 contiguous")
+    _need(mu.dtype == torch.float32 and mu.numel() == hidden, "token_shift: mu float32 [H]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == hidden,
+          "token_shift: state float32 [slots, H]")
+    _need(out.is_contiguous() and tuple(out.shape) == (n, hidden), "token_shift: out [N, H]")
+    for t in (row_entry, entry_q_start, entry_q_len, entry_slot):
+        _need(t.dtype == torch.int32, "token_shift: int32 metadata")
+    _check(_lib().ifx_token_shift(_ptr(h32), _ptr(mu), _ptr(state), _ptr(row_entry), _ptr(entry_q_start),
+                                  _ptr(entry_q_len), _ptr(entry_slot), _ptr(out), _code(out), n, hidden, _stream()),
+           "token_shift")
+    return out
+
+
+def embed_sinusoid_layernorm(table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, weight: torch.Tensor,
+                             eps: float, base: float, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = layer norm(table[ids[t]] + P(positions[t])) * weight with
+    P[2i] = sin(pos * base^(-2i/H)), P[2i+1] = cos of the same angle; out float32 [N, H]."""
+    n, (vocab, hidden) = ids.numel(), table.shape
+    _need(ids.dtype == torch.int32 and positions.dtype == torch.int32 and positions.numel() == n,
+          "embed_sinusoid_layernorm: ids and positions int32 [N]")
+    _need(out.dtype == torch.float32 and table.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (n, hidden),
+          "embed_sinusoid_layernorm: contiguous table, out float32 [N, H]")
+    _need(weight.dtype == torch.float32 and weight.numel() == hidden, "embed_sinusoid_layernorm: weight float32 [H]")
+    _check(_lib().ifx_embed_sinusoid_layernorm(_ptr(table), _code(table), _ptr(ids), _ptr(positions), _ptr(weight),
+                                               float(eps), float(base), _ptr(out), n, hidden, vocab, _stream()),
+           "embed_sinusoid_layernorm")
+    return out
+
+
+def polynorm(z: torch.Tensor, bias: Optional[torch.Tensor], coeff: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, z = z + bias first; N
+    divides a row by its root mean square.  z float32 [M, F], coeff float32 [4]."""
+    m, f = z.shape
+    _need(z.dtype == torch.float32 and z.stride(1) == 1, "polynorm: z float32 with unit inner stride")
+    _need(coeff.dtype == torch.float32 and coeff.numel() == 4, "polynorm: four float32 coefficients")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == f, "polynorm: bias float32 [F]")
+    _need(out.is_contiguous() and tuple(out.shape) == (m, f), "polynorm: out [M, F]")
+    _check(_lib().ifx_polynorm(_ptr(z), z.stride(0), _ptr(bias), _ptr(coeff), float(eps), _ptr(out), _code(out), m, f,
+                               _stream()), "polynorm")
+    return out
+
+
+def mingru_segment() -> int:
+    """Tokens per segment of the minGRU scan."""
+    return int(_lib().ifx_mingru_segment())
+
+
+def mingru_scan(proj: torch.Tensor, state: torch.Tensor, out: torch.Tensor, seg_entry: torch.Tensor, seg_t0: torch.Tensor,
+                n_segments: int, entry_first_seg: torch.Tensor, entry_q_start: torch.Tensor, entry_q_len: torch.Tensor,
+                entry_slot: torch.Tensor, n_entries: int, multi: bool) -> torch.Tensor:
+    """The minGRU recurrence over a step: proj float32 [N, 3W] = the stacked
+    projections [z | x | g] of every token, state float32 [slots, W] (read at
+    an entry's first token, written after its last), out [N, W] =
+    S_t * silu(g_t)."""
+    n, w3 = proj.shape
+    width = w3 // 3
+    _need(proj.dtype == torch.float32 and proj.is_contiguous() and w3 == 3 * width, "mingru_scan: proj float32 [N, 3W]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == width,
+          "mingru_scan: state float32 [slots, W]")
+    _need(out.is_contiguous() and tuple(out.shape) == (n, width), "mingru_scan: out [N, W]")
+    for t in (seg_entry, seg_t0, entry_first_seg, entry_q_start, entry_q_len, entry_slot):
+        _need(t.dtype == torch.int32, "mingru_scan: int32 metadata")
+    scratch = torch.empty(3 * n_segments * width, dtype=torch.float32, device=proj.device) if multi else None
+    _check(_lib().ifx_mingru_scan(_ptr(proj), _ptr(state), _ptr(out), _code(out), _ptr(seg_entry), _ptr(seg_t0), n_segments,
+                                  _ptr(entry_first_seg), _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_slot),
+                                  n_entries, width, 1 if multi else 0, _ptr(scratch), _stream()), "mingru_scan")
+    return out
+
+
+def latent_prep(p: torch.Tensor, wq: torch.Tensor, wkv: torch.Tensor, eps: float, q_rank: int, kv_rank: int, n_heads: int,
+                cq: torch.Tensor, cache: torch.Tensor, page_stride: int, page_size: int, slot_map: torch.Tensor,
+                gate: torch.Tensor) -> None:
+    """From a token's stacked down projections p = [query latent | key/value
+    latent | gates] (float32): cq = unit-rms(query latent) * wq, the key/value
+    latent likewise with wkv into the token's place in the paged cache, gate =
+    sigmoid(gates) float32 [N, heads].  cache: the run's latent stream of page 0."""
+    n = p.shape[0]
+    _need(p.dtype == torch.float32 and p.stride(1) == 1 and p.shape[1] == q_rank + kv_rank + n_heads,
+          "latent_prep: p float32 [N, q_rank + kv_rank + heads]")
+    _need(wq.dtype == torch.float32 and wq.numel() == q_rank and wkv.dtype == torch.float32 and wkv.numel() == kv_rank,
+          "latent_prep: norm weights float32")
+    _need(cq.is_contiguous() and tuple(cq.shape) == (n, q_rank) and cq.dtype == cache.dtype, "latent_prep: cq [N, q_rank]")
+    _need(gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (n, n_heads),
+          "latent_prep: gate float32 [N, heads]")
+    _need(slot_map.dtype == torch.int32 and slot_map.numel() >= n, "latent_prep: slot_map int32 [N]")
+    _check(_lib().ifx_latent_prep(_ptr(p), p.stride(0), _ptr(wq), _ptr(wkv), float(eps), q_rank, kv_rank, n_heads,
+                                  _ptr(cq), _ptr(cache), _code(cache), page_stride, page_size, _ptr(slot_map), _ptr(gate),
+                                  n, _stream()), "latent_prep")
+
+
+def _head_layout(t: torch.Tensor, n_heads: int, width: int, what: str):
+    """(row stride, head stride) of a ``[N, heads, width]`` view whose vectors are contiguous."""
+    _need(t.dim() == 3 and t.shape[1] == n_heads and t.shape[2] == width and (t.stride(2) == 1 or width == 1),
+          f"{what}: a [N, heads, width] view with contiguous vectors")
+    return t.stride(0), t.stride(1)
+
+
+def attn_latent_paged(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_stride: int, page_size: int,
+                      block_tables: torch.Tensor, tile_entry: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int,
+                      entry_q_start: torch.Tensor, entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor,
+                      scale: float) -> torch.Tensor:
+    """Causal attention of new tokens over the cached latents, which serve as
+    keys and as values: q float32 ``[N, heads, rank]`` (the queries moved into
+    the latent space; any view whose vectors are contiguous), out of the same
+    shape in the cache's type (the weighted sums of the latents).  Query tiles
+    of 16 tokens are listed by tile_entry / tile_q0."""
+    _need(block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.stride(1) == 1,
+          "attn_latent: block_tables int32 [R, B]")
+    for t in (tile_entry, tile_q0, entry_q_start, entry_q_len, entry_ctx_start):
+        _need(t.dtype == torch.int32, "attn_latent: int32 metadata")
+    _need(q.dtype == torch.float32 and out.dtype == cache.dtype and q.shape == out.shape,
+          "attn_latent: q float32, out of the cache's type, same shape")
+    n_heads, rank = q.shape[1], q.shape[2]
+    _need(1 <= rank <= 1024, f"attn_latent: rank {rank} is outside 1..1024")
+    (q_row, q_head), (o_row, o_head) = _head_layout(q, n_heads, rank, "attn_latent q"), _head_layout(out, n_heads, rank, "attn_latent out")
+    _check(_lib().ifx_attn_latent_paged(_ptr(q), q_row, q_head, _ptr(out), o_row, o_head, _ptr(cache), _code(cache),
+                                        page_stride, page_size, _ptr(block_tables), block_tables.stride(0), _ptr(tile_entry),
+                                        _ptr(tile_q0), n_tiles, _ptr(entry_q_start), _ptr(entry_q_len),
+                                        _ptr(entry_ctx_start), n_heads, rank, float(scale), _stream()), "attn_latent_paged")
+    return out
+
+
+def gate_heads(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, h * width + d] = x[t, h, d] * gate[t, h]: x float32 ``[N, heads,
+    width]`` (any view whose vectors are contiguous), gate float32 [N, heads],
+    out contiguous ``[N, heads * width]`` in any type."""
+    n, n_heads, width = x.shape
+    _need(x.dtype == torch.float32 and gate.dtype == torch.float32 and gate.is_contiguous()
+          and tuple(gate.shape) == (n, n_heads), "gate_heads: x float32 [N, heads, width], gate float32 [N, heads]")
+    _need(out.is_contiguous() and tuple(out.shape) == (n, n_heads * width), "gate_heads: out [N, heads * width]")
+    row, head = _head_layout(x, n_heads, width, "gate_heads x")
+    _check(_lib().ifx_gate_heads(_ptr(x), row, head, _ptr(gate), _ptr(out), _code(out), n, n_heads, width, _stream()),
+           "gate_heads")
+    return out
+
+
+def add_into(residual: torch.Tensor, delta: torch.Tensor, n_partials: int = 1) -> torch.Tensor:
+    """residual (float32 [N, H]) += delta, or the sum of its ``n_partials`` slices [P, N, H] in index order."""
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and delta.is_contiguous()
+          and delta.numel() == n_partials * residual.numel(), "add_into: float32 contiguous residual, delta [P, N, H]")
+    _check(_lib().ifx_add_into(_ptr(residual), _ptr(delta), _code(delta), n_partials, residual.numel(), residual.numel(),
+                               _stream()), "add_into")
+    return residual
+
+
+def add_rows_vector(a: torch.Tensor, b: torch.Tensor, v: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, :] = a[t, :] + b[t, :] + v[:], all float32; out may be a or b."""
+    n, hidden = a.shape
+    for t in (a, b, out):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == (n, hidden), "add_rows_vector: float32 [N, H]")
+    _need(v.dtype == torch.float32 and v.is_contiguous() and v.numel() == hidden, "add_rows_vector: v float32 [H]")
+    _check(_lib().ifx_add_rows_vector(_ptr(a), _ptr(b), _ptr(v), _ptr(out), n, hidden, _stream()), "add_rows_vector")
     return out

@@ -3,12 +3,18 @@ built-in kinds; more can be added with
 :func:`inferflux_b200.config.registry.register_part`."""
 from .base import Part, KVNeed, StateNeed, RunInfo
 from .linear import Linear
-from .norm import RMSNorm
+from .norm import LayerNorm, RMSNorm
 from .position import RotaryHalf
 from .attention import GQAttention
-from .feed_forward import SwiGLU
-from .block import PreNormBlock
-from .embedding import TokenEmbedding, LinearHead
+from .feed_forward import PolyNormFF, SwiGLU
+from .block import JunctionBlock, ParallelBlock, PreNormBlock
+from .embedding import SinusoidNormEmbedding, TokenEmbedding, LinearHead
+from .shift import TokenShift
+from .recurrent import MinGRU
+from .latent_attention import LatentAttention
+from .junction import LoopEntry
 
 __all__ = ["Part", "KVNeed", "StateNeed", "RunInfo", "Linear", "RMSNorm", "RotaryHalf",
-           "GQAttention", "SwiGLU", "PreNormBlock", "TokenEmbedding", "LinearHead"]
+           "GQAttention", "SwiGLU", "PreNormBlock", "TokenEmbedding", "LinearHead", "LayerNorm", "PolyNormFF",
+           "ParallelBlock", "JunctionBlock", "SinusoidNormEmbedding", "TokenShift", "MinGRU", "LatentAttention",
+           "LoopEntry"]

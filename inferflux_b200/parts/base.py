@@ -90,8 +90,14 @@ class Part:
       split-half pairs ``(i, i + r/2)``; any position part that returns such a
       pair serves it.  A mixer with another idea of position defines its own
       object and says so in its docstring.
-    * ``embedding``: ``forward(token_ids) -> float32 [N, hidden]``;
-      ``lm_head``: ``forward(x) -> float32 [rows, vocab]``.
+    * ``embedding``: ``forward_step(ctx) -> float32 [N, hidden]`` (the default
+      calls ``forward(token_ids)``; one that adds positions reads them from
+      ``ctx``); ``lm_head``: ``forward(x) -> float32 [rows, vocab]``.
+    * ``shift``: ``forward(h32, ctx, run) -> Tensor``: mixes every row of the
+      float32 normed rows with the row before it (the request's state slot
+      holds the last row of the step before).
+    * ``junction``: ``forward(residual, ctx, run) -> None``: rewrites the
+      float32 stream in place between layers (a loop's entry, say).
 
     Any part may describe the step for its kernels (:meth:`describe_step`).
     """
@@ -160,10 +166,12 @@ class RunInfo:
     kv_group / kv_index: the cache group and the run's place in it (None for a
     mixer without paged keys and values); writes_kv False = reads another
     run's cache.  states: the run's per-request state tensors
-    ``[max_seqs, *shape]`` by name."""
+    ``[max_seqs, *shape]`` by name.  params: the run's own parameters from
+    the schedule (:class:`~inferflux_b200.config.spec.Run`)."""
 
     run_index: int
     kv_group: Optional[int] = None
     kv_index: Optional[int] = None
     writes_kv: bool = True
     states: Optional[Dict[str, torch.Tensor]] = None
+    params: Optional[Dict[str, Any]] = None

@@ -20,7 +20,9 @@ from typing import Dict, Optional
 import torch
 
 from ..config.registry import register_part
-from .base import RunInfo
+from ..kernels import ops
+from .base import PartialSums, RunInfo
+from .linear import Linear
 
 
 class PreNormBlock:
@@ -50,3 +52,108 @@ class PreNormBlock:
 
 
 register_part("arrangement", "prenorm", PreNormBlock)
+
+
+class ParallelBlock:
+    """One norm, both branches read it, one sum:
+
+        h = norm(residual);   residual += mixer(shift(h)) + feed_forward(h)
+
+    ``shift`` (optional) mixes what the mixer reads with the token before it;
+    the feed-forward reads ``h`` as it is and may be left out of a layer.
+    When mixer and feed-forward both offer ``inner`` (their rows before the
+    output projection) and an output Linear (``o``, ``down``), the two output
+    projections run as one product over the rows side by side,
+    ``[inner_mixer | inner_ff] [W_o | W_down]^T + b_down``, whose float32 sums
+    are the block's pending delta.  In a step of single tokens the residual
+    sum, the norm, the shift and the update of the shift's state are one kernel.
+    """
+
+    family = "arrangement"
+    roles = {"norm": "norm", "shift": "shift", "mixer": "mixer", "feed_forward": "feed_forward"}
+    optional_roles = frozenset({"shift", "feed_forward"})
+    JOINT_OUTPUT = False
+    FUSED_SINGLE = True
+
+    def __init__(self, parts: Dict[str, object], position_name: Optional[str]):
+        self.norm = parts["norm"]
+        self.shift = parts.get("shift")
+        self.mixer = parts["mixer"]
+        self.feed_forward = parts.get("feed_forward")
+        self.position_name = position_name
+        self._joint = None                    # Linear over [W_o | W_down], built at the first step
+
+    def _joint_output(self):
+        """The two output projections as one Linear, if the parts allow it."""
+        if self._joint is None:
+            self._joint = False
+            if not self.JOINT_OUTPUT:
+                return False
+            m, f = self.mixer, self.feed_forward
+            if (f is not None and hasattr(m, "inner") and hasattr(f, "inner") and getattr(m, "o", None) is not None
+                    and getattr(f, "down", None) is not None and m.o.bias is None
+                    and m.o.weight.dtype == f.down.weight.dtype):
+                self._joint = Linear(torch.cat([m.o.weight, f.down.weight], dim=1), f.down.bias)
+                self._widths = (m.o.in_features, f.down.in_features)
+                m.o = f.down = None           # the joint matrix replaces them
+        return self._joint
+
+    def forward(self, residual: torch.Tensor, delta, ctx, run: RunInfo):
+        n = residual.shape[0]
+        position = ctx.position_tables.get(self.position_name) if self.position_name else None
+        if self.shift is None:
+            h = hs = self.norm.forward(residual, delta)
+        elif self.FUSED_SINGLE and ctx.max_q_len == 1 and hasattr(self.norm, "weight") and hasattr(self.shift, "mu"):
+            n_partials = 1
+            if isinstance(delta, PartialSums):
+                delta, n_partials = delta.tensor, delta.count
+            h = torch.empty((n, residual.shape[1]), dtype=ctx.dtype, device=residual.device)
+            hs = torch.empty_like(h)
+            ops.add_layernorm_shift1(residual, delta, self.norm.weight, self.norm.eps, self.shift.mu,
+                                     run.states["shift_prev"], ctx.entry_slot, h, hs, n_partials)
+        elif ctx.dtype == torch.float32:
+            h = self.norm.forward(residual, delta)
+            hs = self.shift.forward(h, ctx, run)
+        else:
+            h32 = torch.empty((n, residual.shape[1]), dtype=torch.float32, device=residual.device)
+            h = self.norm.forward(residual, delta, out32=h32)
+            hs = self.shift.forward(h32, ctx, run)
+        joint = self._joint_output()
+        if joint:
+            wm, wf = self._widths
+            both = torch.empty((n, wm + wf), dtype=ctx.dtype, device=residual.device)
+            self.mixer.inner(hs, ctx, run, position, out=both[:, :wm])
+            self.feed_forward.inner(h, ctx, out=both[:, wm:])
+            return joint.forward(both, out_dtype=torch.float32, allow_partials=True, f32_sums=True)
+        a = self.mixer.forward(hs, ctx, run, position)
+        if self.feed_forward is None:
+            return a
+        f = self.feed_forward.forward(h, ctx)
+        dense = lambda y: y.tensor.sum(0) if isinstance(y, PartialSums) else y.float()
+        return dense(a).add_(dense(f))
+
+
+class JunctionBlock:
+    """An arrangement that is no layer: the pending delta goes into the stream,
+    then its one part (family ``junction``) rewrites the stream in place."""
+
+    family = "arrangement"
+    roles = {"junction": "junction"}
+    optional_roles = frozenset()
+    needs_embedding_output = True
+
+    def __init__(self, parts: Dict[str, object], position_name: Optional[str]):
+        self.junction = parts["junction"]
+
+    def forward(self, residual: torch.Tensor, delta, ctx, run: RunInfo):
+        if delta is not None:
+            n_partials = 1
+            if isinstance(delta, PartialSums):
+                delta, n_partials = delta.tensor, delta.count
+            ops.add_into(residual, delta, n_partials)
+        self.junction.forward(residual, ctx, run)
+        return None
+
+
+register_part("arrangement", "parallel", ParallelBlock)
+register_part("arrangement", "junction", JunctionBlock)

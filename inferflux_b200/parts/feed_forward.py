@@ -18,7 +18,7 @@ import torch
 
 from ..config.registry import register_part
 from ..kernels import ops
-from ..weights.loader import MATRIX, WeightSpec
+from ..weights.loader import MATRIX, VECTOR, WeightSpec
 from .base import Part
 from .linear import Linear
 
@@ -70,4 +70,52 @@ class SwiGLU(Part):
         return self.down.forward(act, out_dtype=x.dtype, allow_partials=True)
 
 
+class PolyNormFF(Part):
+    """``down( act( up(x) + b_up ) ) + b_down`` with the PolyNorm activation
+
+        act(z) = a N(z) + b N(z^2) + c N(z^3) + e,   N(v) = v / sqrt(mean(v^2) + eps) over a token's row,
+
+    powers taken element by element; a, b, c, e are four numbers of the layer.
+    The up projection leaves float32 sums; bias, the three mean squares and the
+    activation are one kernel in float32.  params: ``hidden``, ``intermediate``,
+    ``eps``, ``name`` (tensors ``<prefix>.<name>.{up,up.b,down,down.b,act}``)."""
+
+    family = "feed_forward"
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
+        self.eps = float(params["eps"])
+        self.up: Linear = None
+        self.up_bias: torch.Tensor = None
+        self.down: Linear = None
+        self.coeff: torch.Tensor = None
+
+    @classmethod
+    def weight_specs(cls, params: Dict[str, Any], prefix: str) -> List[WeightSpec]:
+        h, i = int(params["hidden"]), int(params["intermediate"])
+        n = lambda leaf: cls.full_name(prefix, params, leaf)
+        return [WeightSpec(n("up"), (i, h), MATRIX), WeightSpec(n("up.b"), (i,), VECTOR),
+                WeightSpec(n("down"), (h, i), MATRIX), WeightSpec(n("down.b"), (h,), VECTOR),
+                WeightSpec(n("act"), (4,), VECTOR, std=0.5)]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
+        self.up = Linear(tensors.pop(n("up")))
+        self.up_bias = tensors.pop(n("up.b")).to(torch.float32).contiguous()
+        self.down = Linear(tensors.pop(n("down")), tensors.pop(n("down.b")))
+        self.coeff = tensors.pop(n("act")).to(torch.float32).contiguous()
+
+    def inner(self, x: torch.Tensor, ctx, out: torch.Tensor = None) -> torch.Tensor:
+        """The activated rows ``[N, intermediate]`` that the down projection takes."""
+        z = self.up.forward(x, out_dtype=torch.float32)
+        if out is None:
+            out = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
+        return ops.polynorm(z, self.up_bias, self.coeff, self.eps, out)
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        return self.down.forward(self.inner(x, ctx), out_dtype=torch.float32)
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "polynorm", PolyNormFF)

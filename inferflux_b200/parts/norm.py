@@ -51,4 +51,46 @@ class RMSNorm(Part):
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows, n_partials)
 
 
+class LayerNorm(Part):
+    """Layer norm with a weight and no bias, fused with the residual sum:
+    ``residual += delta;  out = (r - mean(r)) / sqrt(mean((r - mean(r))^2) + eps) * weight``
+    in float32.  params: ``hidden``, ``eps``, and the weight's name: ``name``
+    (weight is ``<prefix>.<name>.weight``) or ``weight_name`` (the leaf itself,
+    ``<prefix>.<weight_name>``)."""
+
+    family = "norm"
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.hidden = int(params["hidden"])
+        self.eps = float(params["eps"])
+        self.weight: Optional[torch.Tensor] = None
+
+    @classmethod
+    def _weight_name(cls, prefix, params) -> str:
+        if params.get("weight_name"):
+            return ".".join(p for p in (prefix, params["weight_name"]) if p)
+        return cls.full_name(prefix, params, "weight")
+
+    @classmethod
+    def weight_specs(cls, params: Dict[str, Any], prefix: str) -> List[WeightSpec]:
+        return [WeightSpec(cls._weight_name(prefix, params), (int(params["hidden"]),), VECTOR, init="one_plus_normal")]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self._weight_name(self.prefix, self.params)].to(torch.float32).contiguous()
+
+    def forward(self, residual: torch.Tensor, delta, out: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None, out32: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """As :meth:`RMSNorm.forward`; ``out32`` (float32 ``[rows, hidden]``)
+        takes the normed rows unrounded as well."""
+        n_partials = 1
+        if isinstance(delta, PartialSums):
+            delta, n_partials = delta.tensor, delta.count
+        n_rows = rows.numel() if rows is not None else residual.shape[0]
+        if out is None:
+            out = torch.empty((n_rows, self.hidden), dtype=self.dtype, device=residual.device)
+        return ops.add_layernorm(residual, delta, self.weight, self.eps, out, rows, n_partials, out32)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)
