@@ -1,0 +1,361 @@
+// Latent attention on the tensor cores (bfloat16 cache): the kernel of attention_latent.cu with mma.sync.
+//
+// The queries are R-wide vectors in the latent space, one per (token, head); keys and values are the cached
+// latents themselves, shared by all heads.  So the heads of a token are rows of one tile: a block takes BM = 16
+// or 64 consecutive (token, head) rows of one request, holds them as bfloat16 in shared memory, and walks the
+// request's pages in tiles of 64 latents that it copies once (cp.async, two buffers) and uses twice:
+//
+//   S = Q C^T      [BM x 64], summed over R       mma.m16n8k16, C read as the col-major operand
+//   P = softmax tile by tile in float32 (running maximum and sum per row, rows rescaled when the maximum moves)
+//   O += P C       [BM x R], summed over 64 keys  the same tile read as the row-major operand (ldmatrix.trans)
+//
+// The eight warps share S by (row tile, key group) and O by columns: every warp owns R/8 columns of all rows,
+// so O never leaves its registers.  S, P and the rows' maxima, sums and rescale factors pass through shared
+// memory.  R is padded with zero columns to a multiple of 64.  With few tiles and long contexts the keys of a
+// tile are cut into splits (blockIdx.y) whose unnormalised sums a second kernel merges.
+//
+// Scores, maxima, sums and O are float32; Q and P enter the products rounded to bfloat16, C is bfloat16 as
+// cached.  Causal: key j is visible to a row whose token is at position p iff j <= p.
+#include "common.cuh"
+
+namespace {
+constexpr int BN = 64;            // latents per tile
+constexpr int PAD = 8;            // bfloat16 elements of padding per shared-memory row (keeps ldmatrix conflict-free)
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x2(unsigned (&r)[2], const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x2_trans(unsigned (&r)[2], const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+struct HeadLayout { long long row, head; };
+
+struct LatentTiles {
+  const int* block_tables;    // [n_entries, bt_stride]
+  int bt_stride;
+  const int* tile_entry;      // [n_tiles]
+  const int* tile_row0;       // [n_tiles] first (token, head) row of the tile within its entry, a multiple of BM
+  const int* entry_q_start;
+  const int* entry_q_len;
+  const int* entry_ctx_start;
+};
+
+// MT: row tiles of 16 per block (BM = 16 MT); RT: R padded to 64 RT columns.
+template <int MT, int RT>
+__global__ void __launch_bounds__(256)
+attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restrict__ out, HeadLayout ol,
+                       const bf16* __restrict__ cache, long long page_stride, int page_size, int page_shift,
+                       LatentTiles b, int n_heads, int rank, float scale, int n_splits,
+                       float* __restrict__ part_o, float* __restrict__ part_ml) {
+  constexpr int BM = 16 * MT, RP = 64 * RT, LD = RP + PAD, LDP = BN + PAD, LDS = BN + 4;
+  constexpr int NT_S = MT;                 // key tiles of 8 per warp in S: 8 warps cover MT x 8 (row tile, key tile) pairs
+  pdl_enter();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                    // [BM][LD]
+  bf16* cs = qs + BM * LD;                                          // [2][BN][LD]
+  bf16* ps = cs + 2 * BN * LD;                                      // [BM][LDP]
+  float* ss = reinterpret_cast<float*>(ps + BM * LDP);              // [BM][LDS]
+  float* row_m = ss + BM * LDS;                                     // [BM]
+  float* row_l = row_m + BM;
+  float* row_a = row_l + BM;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int e = b.tile_entry[tile];
+  const int row0 = b.tile_row0[tile];
+  const int q_len = b.entry_q_len[e];
+  const int n_rows = min(BM, q_len * n_heads - row0);               // rows of the tile that exist
+  const int tok0 = b.entry_q_start[e], pos0 = b.entry_ctx_start[e];
+  const int* bt = b.block_tables + (size_t)e * b.bt_stride;
+  const int last_tok = (row0 + n_rows - 1) / n_heads;
+  const int kend = pos0 + last_tok;                                 // last key any row of the tile may see
+  const int key_tiles = kend / BN + 1;
+  const int per = (key_tiles + n_splits - 1) / n_splits;
+  const int kt_lo = split * per, kt_hi = min(key_tiles, kt_lo + per);
+
+  // zero the padding columns once (no copy ever touches them), load Q as bfloat16
+  for (int idx = tid; idx < (BM + 2 * BN) * (LD - rank); idx += blockDim.x) {
+    const int r = idx / (LD - rank), c = rank + idx % (LD - rank);
+    qs[r * LD + c] = __float2bfloat16_rn(0.0f);                     // qs and cs are contiguous: r runs over both
+  }
+  for (int idx = tid; idx < BM * rank; idx += blockDim.x) {
+    const int r = idx / rank, d = idx - r * rank;
+    float v = 0.0f;
+    if (r < n_rows) {
+      const int rr = row0 + r, t = rr / n_heads, h = rr - t * n_heads;
+      v = q[(size_t)(tok0 + t) * ql.row + (size_t)h * ql.head + d];
+    }
+    qs[r * LD + d] = __float2bfloat16_rn(v);
+  }
+  for (int r = tid; r < BM; r += blockDim.x) { row_m[r] = -INFINITY; row_l[r] = 0.0f; }
+
+  auto load_tile = [&](int kt, int buf) {
+    bf16* dst = cs + (size_t)buf * BN * LD;
+    const int chunks = rank >> 3;                                   // 16-byte chunks per latent
+    for (int idx = tid; idx < BN * chunks; idx += blockDim.x) {
+      const int j = idx / chunks, c = idx - j * chunks;
+      const int key = kt * BN + j;
+      int page = -1;
+      if (key <= kend) page = bt[key >> page_shift];
+      bf16* d = dst + j * LD + c * 8;
+      if (page >= 0)
+        cp_async16(d, cache + (size_t)page * page_stride + (size_t)(key & (page_size - 1)) * rank + c * 8);
+      else
+        *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+
+  float o[MT][RT][4];
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int n = 0; n < RT; ++n) { o[m][n][0] = o[m][n][1] = o[m][n][2] = o[m][n][3] = 0.0f; }
+
+  const int sm = warp % MT, sg = warp / MT;                         // this warp's row tile and key group in S
+  if (kt_lo < kt_hi) load_tile(kt_lo, 0);
+  cp_async_commit();
+  for (int kt = kt_lo; kt < kt_hi; ++kt) {
+    const int buf = (kt - kt_lo) & 1;
+    if (kt + 1 < kt_hi) load_tile(kt + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();                                                // tile kt has landed; Q and the row state are written
+    const bf16* ct = cs + (size_t)buf * BN * LD;
+    // ---- S = Q C^T for this warp's (row tile, key tiles)
+    float s[NT_S][4];
+#pragma unroll
+    for (int j = 0; j < NT_S; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
+    for (int k = 0; k < RP / 16; ++k) {
+      unsigned a[4];
+      ldsm_x4(a, qs + (sm * 16 + (lane & 15)) * LD + k * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int j = 0; j < NT_S; ++j) {
+        unsigned bb[2];
+        const int key0 = (sg * NT_S + j) * 8;
+        ldsm_x2(bb, ct + (key0 + (lane & 7)) * LD + k * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[j], a, bb[0], bb[1]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NT_S; ++j) {
+      const int col = (sg * NT_S + j) * 8 + 2 * tq;
+      float* d0 = ss + (sm * 16 + g) * LDS + col;
+      float* d1 = ss + (sm * 16 + g + 8) * LDS + col;
+      d0[0] = s[j][0]; d0[1] = s[j][1]; d1[0] = s[j][2]; d1[1] = s[j][3];
+    }
+    __syncthreads();
+    // ---- softmax of the tile: a warp takes BM / 8 rows, a lane two keys of a row
+    for (int r = warp * (BM / 8); r < (warp + 1) * (BM / 8); ++r) {
+      const int rr = row0 + r;
+      const int p = pos0 + rr / n_heads;
+      const int key = kt * BN + 2 * lane;
+      const bool v0 = r < n_rows && key <= p, v1 = r < n_rows && key + 1 <= p;
+      const float s0 = v0 ? ss[r * LDS + 2 * lane] * scale : -INFINITY;
+      const float s1 = v1 ? ss[r * LDS + 2 * lane + 1] * scale : -INFINITY;
+      const float m_old = row_m[r];
+      const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
+      float p0 = 0.0f, p1 = 0.0f, alpha = 1.0f;
+      if (m_new != -INFINITY) {
+        alpha = expf(m_old - m_new);
+        p0 = v0 ? expf(s0 - m_new) : 0.0f;
+        p1 = v1 ? expf(s1 - m_new) : 0.0f;
+      }
+      const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+      *reinterpret_cast<__nv_bfloat162*>(ps + r * LDP + 2 * lane) = pp;
+      // the sum is taken over the weights as they enter the product
+      const float sum = warp_sum(__low2float(pp) + __high2float(pp));
+      if (lane == 0) { row_m[r] = m_new; row_l[r] = row_l[r] * alpha + sum; row_a[r] = alpha; }
+    }
+    __syncthreads();
+    // ---- O = O * alpha + P C for this warp's columns
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      const float a0 = row_a[m * 16 + g], a1 = row_a[m * 16 + g + 8];
+#pragma unroll
+      for (int n = 0; n < RT; ++n) { o[m][n][0] *= a0; o[m][n][1] *= a0; o[m][n][2] *= a1; o[m][n][3] *= a1; }
+    }
+#pragma unroll
+    for (int k = 0; k < BN / 16; ++k) {
+      unsigned pa[MT][4];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) ldsm_x4(pa[m], ps + (m * 16 + (lane & 15)) * LDP + k * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int n = 0; n < RT; ++n) {
+        unsigned bb[2];
+        ldsm_x2_trans(bb, ct + (k * 16 + (lane & 15)) * LD + (warp * RT + n) * 8);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) mma_bf16(o[m][n], pa[m], bb[0], bb[1]);
+      }
+    }
+    __syncthreads();                                                // the tile's buffer, S and P may be written again
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- output: normalised rows, or this split's unnormalised sums with their maxima and sums
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = m * 16 + g + 8 * half;
+      if (r >= n_rows) continue;
+      const int rr = row0 + r, t = rr / n_heads, h = rr - t * n_heads;
+      if (n_splits == 1) {
+        const float l = row_l[r];
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        bf16* orow = out + (size_t)(tok0 + t) * ol.row + (size_t)h * ol.head;
+#pragma unroll
+        for (int n = 0; n < RT; ++n) {
+          const int col = (warp * RT + n) * 8 + 2 * tq;
+          if (col < rank)          // rank is a multiple of 8: col + 1 < rank too
+            *reinterpret_cast<__nv_bfloat162*>(orow + col) = __floats2bfloat162_rn(o[m][n][2 * half] * inv, o[m][n][2 * half + 1] * inv);
+        }
+      } else {
+        float* prow = part_o + ((size_t)(tile * n_splits + split) * BM + r) * rank;
+#pragma unroll
+        for (int n = 0; n < RT; ++n) {
+          const int col = (warp * RT + n) * 8 + 2 * tq;
+          if (col < rank) { prow[col] = o[m][n][2 * half]; prow[col + 1] = o[m][n][2 * half + 1]; }
+        }
+      }
+    }
+  }
+  if (n_splits > 1)
+    for (int r = tid; r < n_rows; r += blockDim.x) {
+      float* ml = part_ml + ((size_t)(tile * n_splits + split) * BM + r) * 2;
+      ml[0] = row_m[r];
+      ml[1] = row_l[r];
+    }
+}
+
+// One block per (tile, row): the splits' sums brought to a common maximum and added.
+__global__ void attn_latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         bf16* __restrict__ out, HeadLayout ol, LatentTiles b, int n_heads, int rank,
+                                         int n_splits, int bm) {
+  pdl_enter();
+  const int tile = blockIdx.x, r = blockIdx.y;
+  const int e = b.tile_entry[tile], row0 = b.tile_row0[tile];
+  const int rr = row0 + r;
+  if (rr >= b.entry_q_len[e] * n_heads) return;
+  const int t = rr / n_heads, h = rr - t * n_heads;
+  float mx = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, part_ml[((size_t)(tile * n_splits + s) * bm + r) * 2]);
+  float l = 0.0f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float* ml = part_ml + ((size_t)(tile * n_splits + s) * bm + r) * 2;
+    if (ml[0] != -INFINITY) l += ml[1] * expf(ml[0] - mx);
+  }
+  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+  bf16* orow = out + (size_t)(b.entry_q_start[e] + t) * ol.row + (size_t)h * ol.head;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float acc = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+      const size_t at = (size_t)(tile * n_splits + s) * bm + r;
+      const float m = part_ml[at * 2];
+      if (m != -INFINITY) acc += part_o[at * rank + d] * expf(m - mx);
+    }
+    orow[d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int MT, int RT>
+size_t smem_bytes() {
+  constexpr int BM = 16 * MT, LD = 64 * RT + PAD;
+  return (size_t)(BM + 2 * BN) * LD * 2 + (size_t)BM * (BN + PAD) * 2 + (size_t)BM * (BN + 4) * 4 + (size_t)3 * BM * 4;
+}
+
+template <int MT, int RT>
+int launch_mma(const float* q, HeadLayout ql, bf16* out, HeadLayout ol, const bf16* cache, long long page_stride,
+               int page_size, LatentTiles b, int n_tiles, int n_heads, int rank, float scale, int n_splits,
+               float* part_o, float* part_ml, cudaStream_t stream) {
+  const size_t smem = smem_bytes<MT, RT>();
+  auto kern = attn_latent_mma_kernel<MT, RT>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  int rc = launch_pdl(kern, dim3(n_tiles, n_splits), dim3(256), smem, stream, q, ql, out, ol, cache, page_stride, page_size,
+                      page_shift, b, n_heads, rank, scale, n_splits, part_o, part_ml);
+  if (rc) return rc;
+  if (n_splits > 1) {
+    rc = launch_pdl(attn_latent_merge_kernel, dim3(n_tiles, 16 * MT), dim3(rank >= 256 ? 128 : 64), 0, stream,
+                    (const float*)part_o, (const float*)part_ml, out, ol, b, n_heads, rank, n_splits, 16 * MT);
+    if (rc) return rc;
+  }
+  return IFX_LAUNCH_CHECK();
+}
+}  // namespace
+
+// The largest rank the kernel takes (multiples of 8 up to it).
+IFX_API int ifx_attn_latent_mma_max_rank() { return 512; }
+
+// Into how many splits the keys of every tile are cut: enough blocks to fill the GPU (as many as it holds at
+// this rank's shared memory), but no split shorter than two key tiles.
+IFX_API int ifx_attn_latent_mma_plan(int n_tiles, int bm, int rank, int max_keys) {
+  if (n_tiles <= 0) return 1;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int rt = (rank + 63) / 64;
+  const size_t smem = (size_t)(bm + 2 * BN) * (64 * rt + PAD) * 2 + (size_t)bm * (BN + PAD) * 2 + (size_t)bm * (BN + 4) * 4 + 3 * bm * 4;
+  int per_sm = (int)((size_t)(227 * 1024) / (smem + 1024));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+  const int key_tiles = (max_keys + BN - 1) / BN;
+  int splits = (sms * per_sm) / n_tiles;
+  if (splits > key_tiles / 2) splits = key_tiles / 2;
+  return splits < 1 ? 1 : (splits > 64 ? 64 : splits);
+}
+
+// q float32 and out bfloat16 hold a (token, head) vector at token * row + head * head elements.  Tiles: bm (16 or
+// 64) consecutive (token, head) rows of one entry, listed by tile_entry / tile_row0.  n_splits > 1: part_o holds
+// n_tiles * n_splits * bm * rank floats, part_ml n_tiles * n_splits * bm * 2.
+IFX_API int ifx_attn_latent_mma(const float* q, long long q_row, long long q_head, void* out, long long o_row,
+                                long long o_head, const void* cache, long long page_stride, int page_size,
+                                const int* block_tables, int bt_stride, const int* tile_entry, const int* tile_row0,
+                                int n_tiles, int bm, const int* entry_q_start, const int* entry_q_len,
+                                const int* entry_ctx_start, int n_heads, int rank, float scale, int n_splits,
+                                float* part_o, float* part_ml, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (rank < 8 || rank > 512 || rank % 8 || n_heads < 1 || n_splits < 1 || n_splits > 65535) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1)) || (page_stride & 7)) return IFX_ERR_UNSUPPORTED;
+  if (((uintptr_t)cache & 15) != 0) return IFX_ERR_ALIGNMENT;
+  if (n_splits > 1 && (!part_o || !part_ml)) return IFX_ERR_UNSUPPORTED;
+  LatentTiles b{block_tables, bt_stride, tile_entry, tile_row0, entry_q_start, entry_q_len, entry_ctx_start};
+  HeadLayout ql{q_row, q_head}, ol{o_row, o_head};
+  const int rt = (rank + 63) / 64;
+#define IFX_LM(MT, RT) return launch_mma<MT, RT>(q, ql, (bf16*)out, ol, (const bf16*)cache, page_stride, page_size, b, n_tiles, \
+                                                 n_heads, rank, scale, n_splits, part_o, part_ml, stream)
+  if (bm == 16) {
+    if (rt <= 1) IFX_LM(1, 1);
+    if (rt <= 2) IFX_LM(1, 2);
+    if (rt <= 4) IFX_LM(1, 4);
+    IFX_LM(1, 8);
+  }
+  if (bm == 64) {
+    if (rt <= 1) IFX_LM(4, 1);
+    if (rt <= 2) IFX_LM(4, 2);
+    if (rt <= 4) IFX_LM(4, 4);
+    IFX_LM(4, 8);
+  }
+#undef IFX_LM
+  return IFX_ERR_UNSUPPORTED;
+}

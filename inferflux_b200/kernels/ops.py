@@ -124,12 +124,18 @@ def _lib():
         lib.ifx_attn_latent_paged.argtypes = [c_void_p, c_ll, c_ll, c_void_p, c_ll, c_ll, c_void_p, c_int, c_ll, c_int,
                                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                               c_int, c_int, c_float, c_void_p]
+        lib.ifx_attn_latent_mma.argtypes = [c_void_p, c_ll, c_ll, c_void_p, c_ll, c_ll, c_void_p, c_ll, c_int, c_void_p, c_int,
+                                            c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                            c_float, c_int, c_void_p, c_void_p, c_void_p]
+        lib.ifx_attn_latent_mma_plan.argtypes = [c_int, c_int, c_int, c_int]
+        lib.ifx_attn_latent_mma_max_rank.argtypes = []
         lib.ifx_add_into.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_void_p]
         lib.ifx_add_rows_vector.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.ifx_gate_heads.argtypes = [c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         for name in ("ifx_add_layernorm", "ifx_add_layernorm_shift1", "ifx_token_shift", "ifx_embed_sinusoid_layernorm",
                      "ifx_polynorm", "ifx_mingru_segment", "ifx_mingru_scan", "ifx_latent_prep", "ifx_attn_latent_paged", "ifx_gate_heads",
-                     "ifx_add_into", "ifx_add_rows_vector"):
+                     "ifx_add_into", "ifx_add_rows_vector", "ifx_attn_latent_mma", "ifx_attn_latent_mma_plan",
+                     "ifx_attn_latent_mma_max_rank"):
             getattr(lib, name).restype = c_int
         _sigs_done = True
     return lib
@@ -1030,4 +1036,46 @@ def add_rows_vector(a: torch.Tensor, b: torch.Tensor, v: torch.Tensor, out: torc
         _need(t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == (n, hidden), "add_rows_vector: float32 [N, H]")
     _need(v.dtype == torch.float32 and v.is_contiguous() and v.numel() == hidden, "add_rows_vector: v float32 [H]")
     _check(_lib().ifx_add_rows_vector(_ptr(a), _ptr(b), _ptr(v), _ptr(out), n, hidden, _stream()), "add_rows_vector")
+    return out
+
+
+LATENT_MMA_TILES = (16, 64)      # (token, head) rows per tile of the tensor-core latent attention kernel
+
+
+def attn_latent_mma_ok(rank: int, cache: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel takes this cache: bfloat16, a rank that is a multiple of 8 and not too large."""
+    return cache.dtype == torch.bfloat16 and rank % 8 == 0 and 8 <= rank <= int(_lib().ifx_attn_latent_mma_max_rank())
+
+
+def attn_latent_mma_splits(n_tiles: int, bm: int, rank: int, max_keys: int) -> int:
+    return int(_lib().ifx_attn_latent_mma_plan(n_tiles, bm, rank, max_keys))
+
+
+def attn_latent_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_stride: int, page_size: int,
+                    block_tables: torch.Tensor, tile_entry: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, bm: int,
+                    entry_q_start: torch.Tensor, entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor, scale: float,
+                    n_splits: int = 1) -> torch.Tensor:
+    """:func:`attn_latent_paged` on the tensor cores, bfloat16 cache and result.
+    A tile is ``bm`` (16 or 64) consecutive (token, head) rows of one entry,
+    counted token by token with the heads innermost; ``tile_row0`` is a tile's
+    first row within its entry.  With ``n_splits`` > 1 every tile's keys are cut
+    into that many parts, which a second kernel merges."""
+    _need(block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.stride(1) == 1,
+          "attn_latent_mma: block_tables int32 [R, B]")
+    for t in (tile_entry, tile_row0, entry_q_start, entry_q_len, entry_ctx_start):
+        _need(t.dtype == torch.int32, "attn_latent_mma: int32 metadata")
+    _need(q.dtype == torch.float32 and out.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and q.shape == out.shape,
+          "attn_latent_mma: q float32, out and cache bfloat16")
+    _need(bm in LATENT_MMA_TILES, "attn_latent_mma: tiles of 16 or 64 rows")
+    n_heads, rank = q.shape[1], q.shape[2]
+    (q_row, q_head), (o_row, o_head) = _head_layout(q, n_heads, rank, "attn_latent_mma q"), _head_layout(out, n_heads, rank, "attn_latent_mma out")
+    _need(o_row % 2 == 0 and o_head % 2 == 0, "attn_latent_mma: out vectors on 4-byte boundaries")
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty(n_tiles * n_splits * bm * rank, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(n_tiles * n_splits * bm * 2, dtype=torch.float32, device=q.device)
+    _check(_lib().ifx_attn_latent_mma(_ptr(q), q_row, q_head, _ptr(out), o_row, o_head, _ptr(cache), page_stride, page_size,
+                                      _ptr(block_tables), block_tables.stride(0), _ptr(tile_entry), _ptr(tile_row0), n_tiles,
+                                      bm, _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_ctx_start), n_heads, rank,
+                                      float(scale), n_splits, _ptr(part_o), _ptr(part_ml), _stream()), "attn_latent_mma")
     return out

@@ -33,11 +33,17 @@ QUERY_TILE = 16     # tokens per query tile of the latent attention kernel
 
 @dataclass
 class LatentStep:
-    """The step's query tiles: int32 device tensors."""
+    """The step's query tiles: int32 device tensors.  For the float32 kernel
+    tiles of QUERY_TILE tokens; for the tensor-core kernel tiles of ``bm``
+    (token, head) rows, which depend on the number of heads."""
 
     tile_entry: torch.Tensor
     tile_q0: torch.Tensor
     n_tiles: int
+    bm: int
+    row_tile_entry: torch.Tensor
+    row_tile_row0: torch.Tensor
+    n_row_tiles: int
 
 
 class LatentAttention(Part):
@@ -46,12 +52,12 @@ class LatentAttention(Part):
     ``name`` (tensors ``<prefix>.<name>.{dq,dq.norm,uq,dkv,dkv.norm,uk,uv,g,o}``)."""
 
     family = "mixer"
-    describe_key = "latent_attention"
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
         p = params
         self.hidden, self.heads = int(p["hidden"]), int(p["heads"])
+        self.describe_key = f"latent_attention/{self.heads}"     # layers with as many heads share a step's description
         self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
         self.kv_rank, self.q_rank = int(p["kv_rank"]), int(p["q_rank"])
         self.scale, self.eps = float(p["scale"]), float(p["eps"])
@@ -96,7 +102,14 @@ class LatentAttention(Part):
         for i in range(layout.n_entries):
             for q0 in range(0, int(layout.q_len[i]), QUERY_TILE):
                 tile_entry.append(i), tile_q0.append(q0)
-        return LatentStep(put(tile_entry), put(tile_q0), len(tile_entry))
+        small, large = ops.LATENT_MMA_TILES
+        rows = [int(n) * self.heads for n in layout.q_len[:layout.n_entries]]
+        bm = small if max(rows) <= small else large
+        row_entry, row0 = [], []
+        for i, n in enumerate(rows):
+            for r in range(0, n, bm):
+                row_entry.append(i), row0.append(r)
+        return LatentStep(put(tile_entry), put(tile_q0), len(tile_entry), bm, put(row_entry), put(row0), len(row_entry))
 
     def _per_head(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """x ``[N, heads, a]`` (a view), w ``[heads, b, a]`` -> float32 ``[N, heads, b]``
@@ -126,9 +139,15 @@ class LatentAttention(Part):
         q = self.uq.forward(cq, out_dtype=x.dtype).view(n, self.heads, self.dim)
         q_lat = self._per_head(q, self.uk_t)                                   # float32 [N, heads, kv_rank]
         o_lat = torch.empty((self.heads, n, self.kv_rank), dtype=x.dtype, device=x.device).transpose(0, 1)
-        ops.attn_latent_paged(q_lat, o_lat, cache, page_stride, ctx.page_size, ctx.block_tables[g], step.tile_entry,
-                              step.tile_q0, step.n_tiles, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start,
-                              self.scale)
+        if ops.attn_latent_mma_ok(self.kv_rank, cache):
+            splits = ops.attn_latent_mma_splits(step.n_row_tiles, step.bm, self.kv_rank, ctx.max_ctx_len)
+            ops.attn_latent_mma(q_lat, o_lat, cache, page_stride, ctx.page_size, ctx.block_tables[g], step.row_tile_entry,
+                                step.row_tile_row0, step.n_row_tiles, step.bm, ctx.entry_q_start, ctx.entry_q_len,
+                                ctx.entry_ctx_start, self.scale, splits)
+        else:
+            ops.attn_latent_paged(q_lat, o_lat, cache, page_stride, ctx.page_size, ctx.block_tables[g], step.tile_entry,
+                                  step.tile_q0, step.n_tiles, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start,
+                                  self.scale)
         heads = self._per_head(o_lat, self.uv)                                 # float32 [N, heads, vdim]
         if out is None:
             out = torch.empty((n, self.heads * self.vdim), dtype=x.dtype, device=x.device)

@@ -117,3 +117,69 @@ def rel_err(got, ref) -> float:
     got = torch.as_tensor(np.asarray(got), dtype=torch.float64)
     ref = torch.as_tensor(np.asarray(ref), dtype=torch.float64)
     return float((got - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+
+
+# ------------------------------------------------------------------ Kunonex
+def _kx_attn(heads, dim, vdim, kv_rank, q_rank, scale, ff=None):
+    return dict(type="latent_attention", mixer=dict(heads=heads, dim=dim, vdim=vdim, kv_rank=kv_rank, q_rank=q_rank, scale=scale),
+                mlp=dict(kind="dense", ff=ff) if ff else None)
+
+
+def _kx_gru(width, ff=None):
+    return dict(type="mingru", mixer=dict(width=width), mlp=dict(kind="dense", ff=ff) if ff else None)
+
+
+# Tiny Kunonex configurations that differ in every size and option: dim != vdim, q_rank != heads * dim, ranks
+# that are no multiple of 32, one head, a layer without feed-forward, a loop over a recurrent layer (every pass
+# has a state of its own), a loop that starts at layer 0, a loop that runs once, no loop, other constants.
+KX_A = dict(architecture="Kunonex", width=64, vocab=300, norm=dict(eps=1e-5), logit_scale=0.25,
+            layers=[_kx_attn(3, 24, 16, 40, 56, 0.31, ff=96), _kx_gru(64, ff=80), _kx_attn(1, 32, 48, 24, 20, 0.2),
+                    _kx_gru(48, ff=72)],
+            loop=dict(start=1, stop=3, times=2))
+KX_B = dict(architecture="Kunonex", width=96, vocab=411, norm=dict(eps=3e-6), logit_scale=1.5,
+            layers=[_kx_gru(200, ff=136), _kx_attn(5, 16, 8, 72, 32, 0.5, ff=100), _kx_attn(2, 40, 40, 96, 104, 0.11, ff=64)],
+            loop=dict(start=0, stop=2, times=3))
+KX_C = dict(architecture="Kunonex", width=40, vocab=97, norm=dict(eps=1e-6), logit_scale=1.0,
+            layers=[_kx_attn(2, 8, 12, 16, 16, 0.7, ff=64), _kx_gru(24), _kx_attn(4, 12, 4, 33, 28, 0.4, ff=48)], loop=None)
+KX_D = dict(KX_C, loop=dict(start=2, stop=3, times=1), logit_scale=2.0)
+KX = {"A": KX_A, "B": KX_B, "C": KX_C, "D": KX_D}
+
+
+def kunonex_tensors(cfg: dict, seed: int, sharpen: float = 6.0, lively: float = 12.0):
+    """Random tensors (bfloat16 matrices) for a Kunonex configuration.  ``sharpen`` multiplies the query
+    up-projections so that attention is peaked on single keys, wherever they lie (with N(0, 0.02) weights it is
+    nearly uniform and a lost key among hundreds would hide below the bfloat16 tolerance); ``lively`` multiplies
+    the recurrence's gate projections so that its gates leave the middle and its state matters."""
+    from inferflux_b200.config import load_config
+    from inferflux_b200.config.registry import build_spec
+    from inferflux_b200.engine.model import Model
+    from inferflux_b200.weights.random_init import random_tensors
+    config = load_config(dict(cfg))
+    specs = Model(build_spec(config), torch.float32, "cpu").weight_specs()
+    tensors = random_tensors(specs, seed, torch.bfloat16, None, "cpu")
+    for name in tensors:
+        f = sharpen if name.endswith((".mix.uq", ".mix.uk")) else lively if name.endswith((".mix.z", ".mix.x", ".mix.g")) else 1.0
+        if name.endswith((".mix.uv", ".mix.o", ".mlp.down", ".mlp.up", ".mix.dq", ".mix.dkv")):
+            f = 4.0
+        if f != 1.0:
+            tensors[name] = (tensors[name].float() * f).to(tensors[name].dtype)
+    return config, tensors
+
+
+def make_kunonex_folder(cfg: dict, seed: int, folder: Optional[str] = None, **kw) -> str:
+    from inferflux_b200.weights.safetensors_io import write_safetensors
+    folder = folder or tempfile.mkdtemp(prefix="ifx_kx_")
+    config, tensors = kunonex_tensors(cfg, seed, **kw)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    return folder
+
+
+def load_kunonex_plain(folder: str):
+    """(config dict, tensors in float64) of a model folder, for the plain implementation."""
+    from inferflux_b200.weights.safetensors_io import SafetensorsFile
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    sf = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    return cfg, {n: sf.tensor(n).double() for n in sf.names()}
