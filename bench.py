@@ -172,6 +172,85 @@ def mixed_workload(args) -> int:
     return 0
 
 
+def kunonex_config(size: str, layers: int):
+    """A Kunonex config.json at the widths of one of the family sizes above: every third layer a minGRU of
+    the model's width, the others latent attention (heads of 128, latents of 512, query latents of three
+    quarters of the width), every layer with a PolyNorm feed-forward of the family's width; no loop."""
+    _, hidden, heads, _, inter, vocab, _ = SIZES[size]
+    attn = dict(type="latent_attention", mixer=dict(heads=heads, dim=128, vdim=128, kv_rank=512, q_rank=hidden * 3 // 4,
+                                                    scale=128 ** -0.5), mlp=dict(kind="dense", ff=inter))
+    gru = dict(type="mingru", mixer=dict(width=hidden), mlp=dict(kind="dense", ff=inter))
+    return dict(architecture="Kunonex", width=hidden, vocab=vocab, norm=dict(eps=1e-6), logit_scale=1.0,
+                layers=[gru if i % 3 == 0 else attn for i in range(layers)], loop=None)
+
+
+def architecture_workload(args) -> int:
+    """--arch kunonex: prefill (one 2,048-token prompt) and decode (batch 8 at the given context) of a Kunonex
+    model beside a Qwen2 model of the same width, layer count, feed-forward width and vocabulary, both with
+    random bfloat16 weights, device-timed with CUDA events after warm-up.  One JSON line."""
+    import torch
+    from inferflux_b200 import Engine, SamplingParams, StepEntry
+    layers = args.layers or 8
+    ctx, batch, T = args.context, args.batch, 2048
+    warmup = max(3, args.warmup)
+    greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
+    out = {"metric": f"prefill and decode tokens/s, Kunonex beside Qwen2 at the {args.size.upper()} widths", "impl": "ours",
+           "n_gpus": 1, "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random token ids",
+           "steps": args.steps, "warmup": warmup,
+           "config": {"layers": layers, "size": args.size, "global_batch": batch, "seq_len": ctx, "prefill_tokens": T,
+                      "l2": "weights and cache exceed L2; no flush"}}
+    for name, cfgd in (("kunonex", kunonex_config(args.size, layers)),
+                       ("qwen2", dict(family_config(args.size), num_hidden_layers=layers))):
+        vocab = cfgd.get("vocab") or cfgd["vocab_size"]
+        eng = Engine.from_config(cfgd, seed=0, dtype="bfloat16", kv_cache_tokens=batch * (ctx + 64) + T, max_seqs=batch + 1,
+                                 max_batch_tokens=4096, max_batch_size=batch, chunked_prefill_tokens=2048,
+                                 max_model_len=ctx + 64)
+        runner = eng.runner
+        gen = torch.Generator().manual_seed(0)
+        toks = torch.randint(0, vocab, (T,), generator=gen).tolist()
+        for i in range(3):
+            runner.step([StepEntry(f"pw{i}", toks, [T - 1])])
+            runner.end(f"pw{i}")
+        torch.cuda.synchronize()
+        sampler = ClockSampler()
+        sampler.start()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record()
+        for i in range(5):
+            runner.step([StepEntry(f"p{i}", toks, [T - 1])])
+            runner.end(f"p{i}")
+        ev[1].record()
+        torch.cuda.synchronize()
+        pms = ev[0].elapsed_time(ev[1]) / 5
+        rids = [f"d{i}" for i in range(batch)]
+        for rid in rids:
+            fill = torch.randint(0, vocab, (ctx - args.steps - warmup,), generator=gen).tolist()
+            for s0 in range(0, len(fill), 2048):
+                runner.step([StepEntry(rid, fill[s0:s0 + 2048], [])])
+        dec = torch.randint(0, vocab, (args.steps + warmup, batch), generator=gen).tolist()
+        for w in range(warmup):
+            runner.step([StepEntry(r, [dec[w][i]], [0]) for i, r in enumerate(rids)])
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record()
+        for s0 in range(args.steps):
+            logits = runner.step([StepEntry(r, [dec[warmup + s0][i]], [0]) for i, r in enumerate(rids)])
+            eng.sampler.sample(logits, [greedy] * batch, [0] * batch, [0] * batch, [[]] * batch)
+        ev[1].record()
+        torch.cuda.synchronize()
+        dms = ev[0].elapsed_time(ev[1]) / args.steps
+        clocks = sampler.stop()
+        out[name] = {"prefill_tokens_per_s": round(T / (pms / 1e3), 1), "prefill_ms": round(pms, 3),
+                     "decode_tokens_per_s": round(batch / (dms / 1e3), 1), "decode_ms_per_step": round(dms, 4),
+                     "weight_bytes": eng.model.weight_bytes, "clocks": clocks}
+        del eng, runner
+        torch.cuda.empty_cache()
+    out["value"] = out["kunonex"]["decode_tokens_per_s"]
+    out["unit"] = "tokens/s"
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -188,8 +267,13 @@ def main() -> int:
     ap.add_argument("--mixed", type=int, default=0, metavar="N",
                     help="instead of the decode step: N requests with prompts of 128 to 2,048 tokens and 256 output "
                          "tokens each through Engine.generate (chunked prompts beside decoding requests)")
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "kunonex"],
+                    help="kunonex: instead of the default workload, a Kunonex model beside a Qwen2 model of equal size "
+                         "(--size, --layers, default 8), prefill and decode")
     args = ap.parse_args()
 
+    if args.arch == "kunonex" and args.impl == "ours":
+        return architecture_workload(args)
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:

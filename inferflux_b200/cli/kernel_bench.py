@@ -28,7 +28,11 @@ from ..kernels import ops
 DEV = "cuda:0"
 KERNELS = ["gemv_qkv", "gemv_o", "gemv_gate_up", "gemv_down", "gemv_lm_head", "attn_decode", "attn_decode_skewed", "attn_prefill",
            "attn_prefill_umma",
-           "add_rmsnorm", "rope_kv", "swiglu", "argmax", "sample"]
+           "add_rmsnorm", "rope_kv", "swiglu", "argmax", "sample",
+           # the kernels of the layer-norm / token-shift / minGRU / latent-attention / PolyNorm parts
+           "add_layernorm", "layernorm_shift1", "token_shift", "embed_sinusoid", "polynorm", "mingru_scan", "latent_prep",
+           "attn_latent_decode", "attn_latent_prefill"]
+LATENT = [512, 1536]   # kv_rank, q_rank of the latent-attention workloads (--latent)
 
 
 PAGE_SIZE = 16      # tokens a page of the attention workloads (--page-size)
@@ -229,6 +233,80 @@ class Case:
                 tk = torch.full((rows,), k, dtype=torch.int32, device=DEV)
                 self.extra.append((label, lambda i, tk=tk, p=p, mp=mp: ops.sample(lg, w, f32(0.8), tk, f32(p), f32(mp),
                                                                                  seeds, ctr, oi)))
+        elif name in ("add_layernorm", "layernorm_shift1", "token_shift"):
+            res, delta = torch.randn(rows, h, device=DEV), torch.randn(2, rows, h, device=DEV)
+            w, mu, o, o2 = torch.ones(h, device=DEV), torch.rand(h, device=DEV), torch.empty(rows, h, **bf), torch.empty(rows, h, **bf)
+            h32, state = torch.randn(rows, h, device=DEV), torch.zeros(rows, h, device=DEV)
+            one, ar = it([1] * rows), it(list(range(rows)))
+            self.n_rot = 1
+            if name == "add_layernorm":          # two float32 slices in, the sum and the normed rows (bfloat16 and float32) out
+                self.bytes = rows * h * (4 + 8 + 4 + 2 + 4)
+                self.run = lambda i: ops.add_layernorm(res, delta, w, 1e-6, o, None, 2, h32)
+            elif name == "layernorm_shift1":     # a step of single tokens: sum, norm, shift and state in one kernel
+                self.bytes = rows * h * (4 + 8 + 4 + 2 + 2 + 8)
+                self.run = lambda i: ops.add_layernorm_shift1(res, delta, w, 1e-6, mu, state, ar, o, o2, 2)
+            else:                                # one request's portion of `rows` tokens
+                self.bytes = rows * h * (4 + 2)
+                meta = (it([0] * rows), it([0]), it([rows]), it([0]))
+                self.run = lambda i: ops.token_shift(h32, mu, state, *meta, o)
+        elif name == "embed_sinusoid":
+            table, w = torch.randn(vocab, h, **bf), torch.ones(h, device=DEV)
+            ids, pos, o = it([i % vocab for i in range(rows)]), it(list(range(rows))), torch.empty(rows, h, device=DEV)
+            self.n_rot, self.bytes = 1, rows * h * 6
+            self.run = lambda i: ops.embed_sinusoid_layernorm(table, ids, pos, w, 1e-6, 10000.0, o)
+        elif name == "polynorm":
+            z, bias, coeff = torch.randn(rows, inter, device=DEV), torch.randn(inter, device=DEV), torch.tensor([0.5, 0.3, 0.2, 0.1], device=DEV)
+            o = torch.empty(rows, inter, **bf)
+            self.n_rot, self.bytes = 1, rows * inter * 6
+            self.run = lambda i: ops.polynorm(z, bias, coeff, 1e-6, o)
+        elif name == "mingru_scan":
+            # rows <= 64: that many requests of one token (a decode step); more: one request's portion
+            seg = ops.mingru_segment()
+            proj, o = torch.randn(rows, 3 * h, device=DEV), torch.empty(rows, h, **bf)
+            if rows <= 64:
+                state, args_ = torch.zeros(rows, h, device=DEV), (it(list(range(rows))), it([0] * rows), rows, it(list(range(rows))),
+                                                                    it(list(range(rows))), it([1] * rows), it(list(range(rows))), rows, False)
+            else:
+                n_seg = (rows + seg - 1) // seg
+                state, args_ = torch.zeros(1, h, device=DEV), (it([0] * n_seg), it([k * seg for k in range(n_seg)]), n_seg, it([0]),
+                                                                 it([0]), it([rows]), it([0]), 1, True)
+            self.n_rot, self.bytes = 1, rows * h * (12 + 2) + (rows * h * 8 if rows > 64 else 0)
+            self.run = lambda i: ops.mingru_scan(proj, state, o, *args_)
+        elif name == "latent_prep":
+            kvr, qr = LATENT
+            ps = PAGE_SIZE
+            p = torch.randn(rows, qr + kvr + nh, device=DEV)
+            pool = torch.zeros((rows + ps - 1) // ps + 1, 1, ps * kvr, **bf)
+            cq, gate = torch.empty(rows, qr, **bf), torch.empty(rows, nh, device=DEV)
+            slots = torch.arange(rows, dtype=torch.int32, device=DEV)
+            self.n_rot, self.bytes = 1, rows * ((qr + kvr + nh) * 4 + (qr + kvr) * 2 + nh * 4)
+            wq, wkv = torch.ones(qr, device=DEV), torch.ones(kvr, device=DEV)
+            self.run = lambda i: ops.latent_prep(p, wq, wkv, 1e-6, qr, kvr, nh, cq, pool[0, 0], pool.stride(0), ps, slots, gate)
+        elif name in ("attn_latent_decode", "attn_latent_prefill"):
+            kvr, _ = LATENT
+            ps = PAGE_SIZE
+            decode = name.endswith("decode")
+            b, q_len, ctx = (rows, 1, context) if decode else (1, rows, context)
+            nblk = (ctx + ps - 1) // ps
+            pages = b * nblk
+            self.n_rot = max(2, int(300e6 // (pages * ps * kvr * 2)) + 1)
+            pools = [torch.randn(pages, 1, ps * kvr, **bf) for _ in range(self.n_rot)]
+            bt = torch.randperm(pages).int().view(b, nblk).to(DEV)
+            n = b * q_len
+            q = torch.randn(nh, n, kvr, device=DEV).transpose(0, 1)
+            out = torch.empty(nh, n, kvr, **bf).transpose(0, 1)
+            qs, ql, cs = it([i * q_len for i in range(b)]), it([q_len] * b), it([ctx - q_len] * b)
+            bm = 16 if q_len * nh <= 16 else 64
+            tiles = [(e, r) for e in range(b) for r in range(0, q_len * nh, bm)]
+            te, tr = it([t[0] for t in tiles]), it([t[1] for t in tiles])
+            splits = ops.attn_latent_mma_splits(len(tiles), bm, kvr, ctx)
+            self.note = f"tiles of {bm} rows, splits={splits}"
+            if decode:
+                self.bytes = b * ctx * kvr * 2               # every cached latent once, whatever the number of heads
+            else:
+                self.flops = 2 * 2 * nh * kvr * sum(ctx - q_len + i + 1 for i in range(q_len))
+            self.run = lambda i: ops.attn_latent_mma(q, out, pools[i][0, 0], pools[i].stride(0), ps, bt, te, tr, len(tiles), bm,
+                                                     qs, ql, cs, kvr ** -0.5, splits)
         else:
             raise SystemExit(f"unknown kernel '{name}'; one of {KERNELS}")
 
@@ -321,8 +399,10 @@ def main(argv=None) -> int:
     ap.add_argument("--sweep", action="store_true", help="time: also other numbers of K parts (small products) and of key splits (decode attention)")
     ap.add_argument("--sizes", default="3584,28,4,128,18944,152064",
                     help="hidden,heads,kv_heads,head_dim,intermediate,vocab")
+    ap.add_argument("--latent", default="512,1536", help="kv_rank,q_rank of the latent-attention workloads")
     args = ap.parse_args(argv)
     globals()["PAGE_SIZE"] = args.page_size
+    LATENT[:] = [int(v) for v in args.latent.split(",")]
     if args.mode == "list":
         print("\n".join(KERNELS))
         return 0

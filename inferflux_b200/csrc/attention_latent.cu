@@ -216,32 +216,74 @@ IFX_API int ifx_latent_prep(const float* p, long long p_stride, const float* wq,
 }
 
 namespace {
-// out[t, h, :] = in[t, h, :] * gate[t, h], from float32 rows laid out by `il` into contiguous [N, heads * width]
-// rows of the engine's type: the per-head output gate, the rounding and the gathering of the heads in one pass.
-template <typename TO>
-__global__ void gate_heads_kernel(const float* __restrict__ in, HeadLayout il, const float* __restrict__ gate,
-                                  TO* __restrict__ out, int n_heads, int width) {
+// out[t, h, :] = in[t, h, :] * gate[t, h], from rows laid out by `il` into contiguous [N, heads * width] rows of
+// the engine's type: the per-head output gate, the rounding and the gathering of the heads in one pass.  With
+// row_entry the kernel takes only the rows of entries that bring more than one token (prompt == 1) or exactly
+// one (prompt == 0) and leaves the others as they are.
+template <typename TI, typename TO>
+__global__ void gate_heads_kernel(const TI* __restrict__ in, HeadLayout il, const float* __restrict__ gate,
+                                  TO* __restrict__ out, int n_heads, int width, const int* __restrict__ row_entry,
+                                  const int* __restrict__ entry_q_len, int prompt) {
   pdl_enter();
   const int row = blockIdx.x;
+  if (row_entry && (entry_q_len[row_entry[row]] > 1) != (prompt != 0)) return;
   const int total = n_heads * width;
   for (int i = threadIdx.x; i < total; i += blockDim.x) {
     const int h = i / width, d = i - h * width;
-    out[(size_t)row * total + i] = Num<TO>::from_f(in[(size_t)row * il.row + (size_t)h * il.head + d] * gate[(size_t)row * n_heads + h]);
+    out[(size_t)row * total + i] = Num<TO>::from_f(Num<TI>::to_f(in[(size_t)row * il.row + (size_t)h * il.head + d]) * gate[(size_t)row * n_heads + h]);
   }
+}
+
+// out[i, :] = the cached latent of (entry g_entry[i], position g_pos[i]), found through the block tables.
+template <typename T>
+__global__ void gather_latents_kernel(const T* __restrict__ cache, long long page_stride, int page_size, int page_shift,
+                                      int rank, const int* __restrict__ block_tables, int bt_stride,
+                                      const int* __restrict__ g_entry, const int* __restrict__ g_pos, T* __restrict__ out) {
+  pdl_enter();
+  const int row = blockIdx.x;
+  const int pos = g_pos[row];
+  const int page = block_tables[(size_t)g_entry[row] * bt_stride + (pos >> page_shift)];
+  const T* src = cache + (size_t)(page < 0 ? 0 : page) * page_stride + (size_t)(pos & (page_size - 1)) * rank;
+  T* dst = out + (size_t)row * rank;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = page < 0 ? Num<T>::from_f(0.0f) : src[i];
 }
 }  // namespace
 
-IFX_API int ifx_gate_heads(const float* in, long long in_row, long long in_head, const float* gate, void* out, int out_dtype,
-                           int n_rows, int n_heads, int width, cudaStream_t stream) {
+// in_dtype / out_dtype: IFX_F32 or IFX_BF16.  row_entry (with entry_q_len) may be null: every row is taken.
+IFX_API int ifx_gate_heads(const void* in, int in_dtype, long long in_row, long long in_head, const float* gate, void* out,
+                           int out_dtype, int n_rows, int n_heads, int width, const int* row_entry,
+                           const int* entry_q_len, int prompt, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   const int total = n_heads * width;
   const int threads = total >= 1024 ? 256 : (total >= 256 ? 128 : 64);
   HeadLayout il{in_row, in_head};
   int rc;
-  if (out_dtype == IFX_F32)
-    rc = launch_pdl(gate_heads_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, in, il, gate, (float*)out, n_heads, width);
-  else if (out_dtype == IFX_BF16)
-    rc = launch_pdl(gate_heads_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, in, il, gate, (bf16*)out, n_heads, width);
+#define IFX_GH(TI, TO) rc = launch_pdl(gate_heads_kernel<TI, TO>, dim3(n_rows), dim3(threads), 0, stream, (const TI*)in, il, gate, \
+                                       (TO*)out, n_heads, width, row_entry, entry_q_len, prompt)
+  if (in_dtype == IFX_F32 && out_dtype == IFX_F32) IFX_GH(float, float);
+  else if (in_dtype == IFX_F32 && out_dtype == IFX_BF16) IFX_GH(float, bf16);
+  else if (in_dtype == IFX_BF16 && out_dtype == IFX_BF16) IFX_GH(bf16, bf16);
+  else if (in_dtype == IFX_BF16 && out_dtype == IFX_F32) IFX_GH(bf16, float);
+  else return IFX_ERR_UNSUPPORTED;
+#undef IFX_GH
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
+IFX_API int ifx_gather_latents(const void* cache, int dtype, long long page_stride, int page_size, int rank,
+                               const int* block_tables, int bt_stride, const int* g_entry, const int* g_pos, void* out,
+                               int n_rows, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (page_size <= 0 || (page_size & (page_size - 1)) || rank < 1) return IFX_ERR_UNSUPPORTED;
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  const int threads = rank >= 256 ? 128 : 64;
+  int rc;
+  if (dtype == IFX_F32)
+    rc = launch_pdl(gather_latents_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (const float*)cache, page_stride,
+                    page_size, page_shift, rank, block_tables, bt_stride, g_entry, g_pos, (float*)out);
+  else if (dtype == IFX_BF16)
+    rc = launch_pdl(gather_latents_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, (const bf16*)cache, page_stride,
+                    page_size, page_shift, rank, block_tables, bt_stride, g_entry, g_pos, (bf16*)out);
   else
     return IFX_ERR_UNSUPPORTED;
   return rc ? rc : IFX_LAUNCH_CHECK();

@@ -77,6 +77,7 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
   float* row_m = ss + BM * LDS;                                     // [BM]
   float* row_l = row_m + BM;
   float* row_a = row_l + BM;
+  int* row_pos = reinterpret_cast<int*>(row_a + BM);                // [BM] position of each row's token, -1 = no such row
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
   const int tile = blockIdx.x, split = blockIdx.y;
   const int e = b.tile_entry[tile];
@@ -105,21 +106,27 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
     }
     qs[r * LD + d] = __float2bfloat16_rn(v);
   }
-  for (int r = tid; r < BM; r += blockDim.x) { row_m[r] = -INFINITY; row_l[r] = 0.0f; }
+  for (int r = tid; r < BM; r += blockDim.x) {
+    row_m[r] = -INFINITY;
+    row_l[r] = 0.0f;
+    row_pos[r] = r < n_rows ? pos0 + (row0 + r) / n_heads : -1;
+  }
 
+  // a warp copies whole latents (one block-table look-up each), its lanes the 16-byte chunks of one
   auto load_tile = [&](int kt, int buf) {
     bf16* dst = cs + (size_t)buf * BN * LD;
-    const int chunks = rank >> 3;                                   // 16-byte chunks per latent
-    for (int idx = tid; idx < BN * chunks; idx += blockDim.x) {
-      const int j = idx / chunks, c = idx - j * chunks;
+    const int chunks = rank >> 3;
+    for (int j = warp; j < BN; j += 8) {
       const int key = kt * BN + j;
       int page = -1;
       if (key <= kend) page = bt[key >> page_shift];
-      bf16* d = dst + j * LD + c * 8;
-      if (page >= 0)
-        cp_async16(d, cache + (size_t)page * page_stride + (size_t)(key & (page_size - 1)) * rank + c * 8);
-      else
-        *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+      bf16* d = dst + j * LD;
+      if (page >= 0) {
+        const bf16* src = cache + (size_t)page * page_stride + (size_t)(key & (page_size - 1)) * rank;
+        for (int c = lane; c < chunks; c += 32) cp_async16(d + c * 8, src + c * 8);
+      } else {
+        for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+      }
     }
   };
 
@@ -143,15 +150,24 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
     float s[NT_S][4];
 #pragma unroll
     for (int j = 0; j < NT_S; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
-    for (int k = 0; k < RP / 16; ++k) {
-      unsigned a[4];
-      ldsm_x4(a, qs + (sm * 16 + (lane & 15)) * LD + k * 16 + (lane >> 4) * 8);
+    {
+      // fragments of step k + 1 are asked for before the products of step k are issued
+      const bf16* qa = qs + (sm * 16 + (lane & 15)) * LD + (lane >> 4) * 8;
+      const bf16* cb = ct + (sg * NT_S * 8 + (lane & 7)) * LD + ((lane >> 3) & 1) * 8;
+      unsigned a[2][4], bb[2][NT_S][2];
+      ldsm_x4(a[0], qa);
 #pragma unroll
-      for (int j = 0; j < NT_S; ++j) {
-        unsigned bb[2];
-        const int key0 = (sg * NT_S + j) * 8;
-        ldsm_x2(bb, ct + (key0 + (lane & 7)) * LD + k * 16 + ((lane >> 3) & 1) * 8);
-        mma_bf16(s[j], a, bb[0], bb[1]);
+      for (int j = 0; j < NT_S; ++j) ldsm_x2(bb[0][j], cb + j * 8 * LD);
+#pragma unroll 2
+      for (int k = 0; k < RP / 16; ++k) {
+        const int cur = k & 1, nxt = cur ^ 1;
+        if (k + 1 < RP / 16) {
+          ldsm_x4(a[nxt], qa + (k + 1) * 16);
+#pragma unroll
+          for (int j = 0; j < NT_S; ++j) ldsm_x2(bb[nxt][j], cb + j * 8 * LD + (k + 1) * 16);
+        }
+#pragma unroll
+        for (int j = 0; j < NT_S; ++j) mma_bf16(s[j], a[cur], bb[cur][j][0], bb[cur][j][1]);
       }
     }
 #pragma unroll
@@ -164,10 +180,9 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
     __syncthreads();
     // ---- softmax of the tile: a warp takes BM / 8 rows, a lane two keys of a row
     for (int r = warp * (BM / 8); r < (warp + 1) * (BM / 8); ++r) {
-      const int rr = row0 + r;
-      const int p = pos0 + rr / n_heads;
+      const int p = row_pos[r];                                      // -1 hides every key from a row that does not exist
       const int key = kt * BN + 2 * lane;
-      const bool v0 = r < n_rows && key <= p, v1 = r < n_rows && key + 1 <= p;
+      const bool v0 = key <= p, v1 = key + 1 <= p;
       const float s0 = v0 ? ss[r * LDS + 2 * lane] * scale : -INFINITY;
       const float s1 = v1 ? ss[r * LDS + 2 * lane + 1] * scale : -INFINITY;
       const float m_old = row_m[r];
@@ -192,17 +207,26 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
 #pragma unroll
       for (int n = 0; n < RT; ++n) { o[m][n][0] *= a0; o[m][n][1] *= a0; o[m][n][2] *= a1; o[m][n][3] *= a1; }
     }
+    {
+      const bf16* pb = ps + (lane & 15) * LDP + (lane >> 4) * 8;
+      const bf16* vb = ct + (lane & 15) * LD + warp * RT * 8;
+      unsigned bb[2][2];
+      ldsm_x2_trans(bb[0], vb);
 #pragma unroll
-    for (int k = 0; k < BN / 16; ++k) {
-      unsigned pa[MT][4];
+      for (int k = 0; k < BN / 16; ++k) {
+        unsigned pa[MT][4];
 #pragma unroll
-      for (int m = 0; m < MT; ++m) ldsm_x4(pa[m], ps + (m * 16 + (lane & 15)) * LDP + k * 16 + (lane >> 4) * 8);
+        for (int m = 0; m < MT; ++m) ldsm_x4(pa[m], pb + m * 16 * LDP + k * 16);
 #pragma unroll
-      for (int n = 0; n < RT; ++n) {
-        unsigned bb[2];
-        ldsm_x2_trans(bb, ct + (k * 16 + (lane & 15)) * LD + (warp * RT + n) * 8);
+        for (int n = 0; n < RT; ++n) {
+          const int at = k * RT + n, cur = at & 1, nxt = cur ^ 1;
+          if (at + 1 < (BN / 16) * RT) {
+            const int k2 = (at + 1) / RT, n2 = (at + 1) % RT;
+            ldsm_x2_trans(bb[nxt], vb + k2 * 16 * LD + n2 * 8);
+          }
 #pragma unroll
-        for (int m = 0; m < MT; ++m) mma_bf16(o[m][n], pa[m], bb[0], bb[1]);
+          for (int m = 0; m < MT; ++m) mma_bf16(o[m][n], pa[m], bb[cur][0], bb[cur][1]);
+        }
       }
     }
     __syncthreads();                                                // the tile's buffer, S and P may be written again
@@ -246,40 +270,51 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
     }
 }
 
-// One block per (tile, row): the splits' sums brought to a common maximum and added.
+// One block per (tile, row): the splits' sums brought to a common maximum and added.  The weight of every split
+// (its share of the common sum) is worked out once per row; the sums of the splits are then read side by side.
 __global__ void attn_latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          bf16* __restrict__ out, HeadLayout ol, LatentTiles b, int n_heads, int rank,
                                          int n_splits, int bm) {
   pdl_enter();
+  __shared__ float w[64];
   const int tile = blockIdx.x, r = blockIdx.y;
   const int e = b.tile_entry[tile], row0 = b.tile_row0[tile];
   const int rr = row0 + r;
   if (rr >= b.entry_q_len[e] * n_heads) return;
   const int t = rr / n_heads, h = rr - t * n_heads;
-  float mx = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, part_ml[((size_t)(tile * n_splits + s) * bm + r) * 2]);
-  float l = 0.0f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float* ml = part_ml + ((size_t)(tile * n_splits + s) * bm + r) * 2;
-    if (ml[0] != -INFINITY) l += ml[1] * expf(ml[0] - mx);
+  const size_t first = (size_t)tile * n_splits * bm + r;             // split s lies s * bm rows further on
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    if (lane < n_splits) { m0 = part_ml[(first + (size_t)lane * bm) * 2]; l0 = part_ml[(first + (size_t)lane * bm) * 2 + 1]; }
+    if (lane + 32 < n_splits) { m1 = part_ml[(first + (size_t)(lane + 32) * bm) * 2]; l1 = part_ml[(first + (size_t)(lane + 32) * bm) * 2 + 1]; }
+    const float mx = warp_max(fmaxf(m0, m1));
+    const float e0 = m0 == -INFINITY ? 0.0f : expf(m0 - mx), e1 = m1 == -INFINITY ? 0.0f : expf(m1 - mx);
+    const float l = warp_sum(l0 * e0 + l1 * e1);
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    w[lane] = e0 * inv;
+    w[lane + 32] = e1 * inv;
   }
-  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+  __syncthreads();
   bf16* orow = out + (size_t)(b.entry_q_start[e] + t) * ol.row + (size_t)h * ol.head;
   for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    const float* p = part_o + first * rank + d;
     float acc = 0.0f;
-    for (int s = 0; s < n_splits; ++s) {
-      const size_t at = (size_t)(tile * n_splits + s) * bm + r;
-      const float m = part_ml[at * 2];
-      if (m != -INFINITY) acc += part_o[at * rank + d] * expf(m - mx);
+    int s = 0;
+    for (; s + 4 <= n_splits; s += 4) {
+      const float v0 = p[(size_t)s * bm * rank], v1 = p[(size_t)(s + 1) * bm * rank];
+      const float v2 = p[(size_t)(s + 2) * bm * rank], v3 = p[(size_t)(s + 3) * bm * rank];
+      acc = fmaf(v3, w[s + 3], fmaf(v2, w[s + 2], fmaf(v1, w[s + 1], fmaf(v0, w[s], acc))));
     }
-    orow[d] = __float2bfloat16_rn(acc * inv);
+    for (; s < n_splits; ++s) acc = fmaf(p[(size_t)s * bm * rank], w[s], acc);
+    orow[d] = __float2bfloat16_rn(acc);
   }
 }
 
 template <int MT, int RT>
 size_t smem_bytes() {
   constexpr int BM = 16 * MT, LD = 64 * RT + PAD;
-  return (size_t)(BM + 2 * BN) * LD * 2 + (size_t)BM * (BN + PAD) * 2 + (size_t)BM * (BN + 4) * 4 + (size_t)3 * BM * 4;
+  return (size_t)(BM + 2 * BN) * LD * 2 + (size_t)BM * (BN + PAD) * 2 + (size_t)BM * (BN + 4) * 4 + (size_t)4 * BM * 4;
 }
 
 template <int MT, int RT>
@@ -298,7 +333,7 @@ int launch_mma(const float* q, HeadLayout ql, bf16* out, HeadLayout ol, const bf
                       page_shift, b, n_heads, rank, scale, n_splits, part_o, part_ml);
   if (rc) return rc;
   if (n_splits > 1) {
-    rc = launch_pdl(attn_latent_merge_kernel, dim3(n_tiles, 16 * MT), dim3(rank >= 256 ? 128 : 64), 0, stream,
+    rc = launch_pdl(attn_latent_merge_kernel, dim3(n_tiles, 16 * MT), dim3(rank > 256 ? 256 : (rank > 64 ? 128 : 64)), 0, stream,
                     (const float*)part_o, (const float*)part_ml, out, ol, b, n_heads, rank, n_splits, 16 * MT);
     if (rc) return rc;
   }
@@ -316,7 +351,7 @@ IFX_API int ifx_attn_latent_mma_plan(int n_tiles, int bm, int rank, int max_keys
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int rt = (rank + 63) / 64;
-  const size_t smem = (size_t)(bm + 2 * BN) * (64 * rt + PAD) * 2 + (size_t)bm * (BN + PAD) * 2 + (size_t)bm * (BN + 4) * 4 + 3 * bm * 4;
+  const size_t smem = (size_t)(bm + 2 * BN) * (64 * rt + PAD) * 2 + (size_t)bm * (BN + PAD) * 2 + (size_t)bm * (BN + 4) * 4 + 4 * bm * 4;
   int per_sm = (int)((size_t)(227 * 1024) / (smem + 1024));
   per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
   const int key_tiles = (max_keys + BN - 1) / BN;
@@ -335,7 +370,7 @@ IFX_API int ifx_attn_latent_mma(const float* q, long long q_row, long long q_hea
                                 const int* entry_ctx_start, int n_heads, int rank, float scale, int n_splits,
                                 float* part_o, float* part_ml, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  if (rank < 8 || rank > 512 || rank % 8 || n_heads < 1 || n_splits < 1 || n_splits > 65535) return IFX_ERR_UNSUPPORTED;
+  if (rank < 8 || rank > 512 || rank % 8 || n_heads < 1 || n_splits < 1 || n_splits > 64) return IFX_ERR_UNSUPPORTED;
   if (page_size <= 0 || (page_size & (page_size - 1)) || (page_stride & 7)) return IFX_ERR_UNSUPPORTED;
   if (((uintptr_t)cache & 15) != 0) return IFX_ERR_ALIGNMENT;
   if (n_splits > 1 && (!part_o || !part_ml)) return IFX_ERR_UNSUPPORTED;

@@ -15,7 +15,7 @@
 // A thread owns one channel; channels are independent.
 #include "common.cuh"
 
-#define IFX_MINGRU_SEGMENT 64
+#define IFX_MINGRU_SEGMENT 32
 
 namespace {
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
@@ -47,6 +47,7 @@ mingru_segment_sums_kernel(GruStep s, float* __restrict__ seg_a, float* __restri
   const int n = min(IFX_MINGRU_SEGMENT, s.entry_q_len[e] - t0);
   const float* row = s.proj + (size_t)(s.entry_q_start[e] + t0) * 3 * s.width;
   float A = 1.0f, B = 0.0f;
+#pragma unroll 8
   for (int t = 0; t < n; ++t, row += 3 * s.width) {
     float a, b;
     gate(row, s.width, ch, a, b);
@@ -87,6 +88,7 @@ mingru_scan_kernel(GruStep s, const float* __restrict__ seg_start, float* __rest
   TO* o = out + row0 * s.width + ch;
   float* st = state + (size_t)s.entry_slot[e] * s.width + ch;
   float S = seg_start ? seg_start[(size_t)seg * s.width + ch] : *st;
+#pragma unroll 8
   for (int t = 0; t < n; ++t, row += 3 * s.width, o += s.width) {
     float a, b;
     gate(row, s.width, ch, a, b);

@@ -35,6 +35,59 @@ __global__ void polynorm_kernel(const float* __restrict__ z, long long z_stride,
     o[i] = Num<TO>::from_f(fmaf(v, r1, fmaf(v2, r2, fmaf(v2 * v, r3, e))));
   }
 }
+
+// The same with 16-byte loads and 8-byte stores: n a multiple of 4, rows and bias on 16-byte boundaries.
+template <typename TO>
+__global__ void polynorm_vec_kernel(const float* __restrict__ z, long long z_stride, const float* __restrict__ bias,
+                                    const float* __restrict__ coeff, float eps, TO* __restrict__ out, int n) {
+  pdl_enter();
+  extern __shared__ float4 row_buf4[];
+  __shared__ float red[32];
+  const float4* zr = reinterpret_cast<const float4*>(z + (size_t)blockIdx.x * z_stride);
+  const float4* b4 = reinterpret_cast<const float4*>(bias);
+  const int groups = n >> 2;
+  float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+  for (int i = threadIdx.x; i < groups; i += blockDim.x) {
+    float4 v = zr[i];
+    if (bias) { const float4 b = b4[i]; v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
+    row_buf4[i] = v;
+    const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float v2 = e[k] * e[k], v3 = v2 * e[k];
+      s1 = fmaf(e[k], e[k], s1);
+      s2 = fmaf(v2, v2, s2);
+      s3 = fmaf(v3, v3, s3);
+    }
+  }
+  s1 = block_sum(s1, red);
+  s2 = block_sum(s2, red);
+  s3 = block_sum(s3, red);
+  const float r1 = coeff[0] / sqrtf(s1 / (float)n + eps);
+  const float r2 = coeff[1] / sqrtf(s2 / (float)n + eps);
+  const float r3 = coeff[2] / sqrtf(s3 / (float)n + eps);
+  const float e0 = coeff[3];
+  TO* o = out + (size_t)blockIdx.x * n;
+  for (int i = threadIdx.x; i < groups; i += blockDim.x) {
+    const float4 v = row_buf4[i];
+    float y[4];
+    const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float v2 = e[k] * e[k];
+      y[k] = fmaf(e[k], r1, fmaf(v2, r2, fmaf(v2 * e[k], r3, e0)));
+    }
+    if constexpr (sizeof(TO) == 4) {
+      reinterpret_cast<float4*>(o)[i] = make_float4(y[0], y[1], y[2], y[3]);
+    } else {
+      __nv_bfloat162 a = __floats2bfloat162_rn(y[0], y[1]), b = __floats2bfloat162_rn(y[2], y[3]);
+      uint2 u;
+      u.x = *reinterpret_cast<unsigned*>(&a);
+      u.y = *reinterpret_cast<unsigned*>(&b);
+      reinterpret_cast<uint2*>(o)[i] = u;
+    }
+  }
+}
 }  // namespace
 
 // z float32 [rows, n] (row stride z_stride), bias float32 [n] or null, coeff float32 [4] = a, b, c, e.
@@ -46,6 +99,23 @@ IFX_API int ifx_polynorm(const float* z, long long z_stride, const float* bias, 
   int threads = 64;
   while (threads < 1024 && threads * 4 < n) threads <<= 1;
   int rc;
+  const bool vec = n % 4 == 0 && (z_stride & 3) == 0 && (((uintptr_t)z | (uintptr_t)bias | (uintptr_t)out) & 15) == 0;
+  if (vec && (out_dtype == IFX_F32 || out_dtype == IFX_BF16)) {
+    threads = 64;
+    while (threads < 1024 && threads * 8 < n) threads <<= 1;
+    if (out_dtype == IFX_F32) {
+      auto kern = polynorm_vec_kernel<float>;
+      if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return (int)cudaGetLastError();
+      rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, z, z_stride, bias, coeff, eps, (float*)out, n);
+    } else {
+      auto kern = polynorm_vec_kernel<bf16>;
+      if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return (int)cudaGetLastError();
+      rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, z, z_stride, bias, coeff, eps, (bf16*)out, n);
+    }
+    return rc ? rc : IFX_LAUNCH_CHECK();
+  }
   if (out_dtype == IFX_F32) {
     auto kern = polynorm_kernel<float>;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)

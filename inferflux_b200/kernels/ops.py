@@ -131,11 +131,14 @@ def _lib():
         lib.ifx_attn_latent_mma_max_rank.argtypes = []
         lib.ifx_add_into.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_void_p]
         lib.ifx_add_rows_vector.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
-        lib.ifx_gate_heads.argtypes = [c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.ifx_gate_heads.argtypes = [c_void_p, c_int, c_ll, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                       c_void_p, c_int, c_void_p]
+        lib.ifx_gather_latents.argtypes = [c_void_p, c_int, c_ll, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                           c_int, c_void_p]
         for name in ("ifx_add_layernorm", "ifx_add_layernorm_shift1", "ifx_token_shift", "ifx_embed_sinusoid_layernorm",
                      "ifx_polynorm", "ifx_mingru_segment", "ifx_mingru_scan", "ifx_latent_prep", "ifx_attn_latent_paged", "ifx_gate_heads",
                      "ifx_add_into", "ifx_add_rows_vector", "ifx_attn_latent_mma", "ifx_attn_latent_mma_plan",
-                     "ifx_attn_latent_mma_max_rank"):
+                     "ifx_attn_latent_mma_max_rank", "ifx_gather_latents"):
             getattr(lib, name).restype = c_int
         _sigs_done = True
     return lib
@@ -1006,17 +1009,34 @@ def attn_latent_paged(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, p
     return out
 
 
-def gate_heads(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, h * width + d] = x[t, h, d] * gate[t, h]: x float32 ``[N, heads,
-    width]`` (any view whose vectors are contiguous), gate float32 [N, heads],
-    out contiguous ``[N, heads * width]`` in any type."""
+def gate_heads(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, row_entry: Optional[torch.Tensor] = None,
+               entry_q_len: Optional[torch.Tensor] = None, prompt_rows: bool = False) -> torch.Tensor:
+    """out[t, h * width + d] = x[t, h, d] * gate[t, h]: x ``[N, heads, width]``
+    (any view whose vectors are contiguous), gate float32 [N, heads], out
+    contiguous ``[N, heads * width]``.  With ``row_entry`` (the entry of every
+    row) and ``entry_q_len`` only the rows of entries with more than one token
+    (``prompt_rows``) or with exactly one are written."""
     n, n_heads, width = x.shape
-    _need(x.dtype == torch.float32 and gate.dtype == torch.float32 and gate.is_contiguous()
-          and tuple(gate.shape) == (n, n_heads), "gate_heads: x float32 [N, heads, width], gate float32 [N, heads]")
+    _need(gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (n, n_heads),
+          "gate_heads: gate float32 [N, heads]")
     _need(out.is_contiguous() and tuple(out.shape) == (n, n_heads * width), "gate_heads: out [N, heads * width]")
     row, head = _head_layout(x, n_heads, width, "gate_heads x")
-    _check(_lib().ifx_gate_heads(_ptr(x), row, head, _ptr(gate), _ptr(out), _code(out), n, n_heads, width, _stream()),
-           "gate_heads")
+    _check(_lib().ifx_gate_heads(_ptr(x), _code(x), row, head, _ptr(gate), _ptr(out), _code(out), n, n_heads, width,
+                                 _ptr(row_entry), _ptr(entry_q_len), 1 if prompt_rows else 0, _stream()), "gate_heads")
+    return out
+
+
+def gather_latents(cache: torch.Tensor, page_stride: int, page_size: int, block_tables: torch.Tensor,
+                   g_entry: torch.Tensor, g_pos: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[i] = the cached latent at position g_pos[i] of entry g_entry[i] (zeros
+    where its page was given back).  cache: the run's latent stream of page 0."""
+    n, rank = out.shape
+    _need(out.is_contiguous() and out.dtype == cache.dtype and cache.shape[-1] == rank, "gather_latents: out [n, rank] of the cache's type")
+    _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1 and g_entry.dtype == torch.int32
+          and g_pos.dtype == torch.int32 and g_entry.numel() >= n and g_pos.numel() >= n, "gather_latents: int32 metadata")
+    _check(_lib().ifx_gather_latents(_ptr(cache), _code(cache), page_stride, page_size, rank, _ptr(block_tables),
+                                     block_tables.stride(0), _ptr(g_entry), _ptr(g_pos), _ptr(out), n, _stream()),
+           "gather_latents")
     return out
 
 

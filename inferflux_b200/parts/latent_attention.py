@@ -29,6 +29,7 @@ from .base import CacheStream, KVNeed, Part, RunInfo
 from .linear import Linear
 
 QUERY_TILE = 16     # tokens per query tile of the latent attention kernel
+PROMPT_PAGE = 64    # tokens per page of the keys and values that a prompt step forms for its own use
 
 
 @dataclass
@@ -44,6 +45,25 @@ class LatentStep:
     row_tile_entry: torch.Tensor
     row_tile_row0: torch.Tensor
     n_row_tiles: int
+    prompt: Optional["PromptStep"] = None     # set when the step's portions go through keys and values per head
+
+
+@dataclass
+class PromptStep:
+    """Prompt portions attended per head (see :meth:`LatentAttention._prompt_by_heads`):
+    which cached latents to expand, where the expanded keys and values of each
+    entry lie, and the query tiles of the tensor-core prompt kernel."""
+
+    g_entry: torch.Tensor                     # [G] entry of every latent to expand (each entry's context, padded to whole pages)
+    g_pos: torch.Tensor                       # [G] its position
+    n_gather: int
+    block_tables: torch.Tensor                # [R, B] pages of the expanded keys and values, -1 for entries without a portion
+    tile_entry: torch.Tensor
+    tile_q0: torch.Tensor
+    n_tiles: int
+    tile_rows: int
+    max_keys: int
+    row_entry: torch.Tensor                   # [N] the entry of every row of the step
 
 
 class LatentAttention(Part):
@@ -57,10 +77,12 @@ class LatentAttention(Part):
         super().__init__(params, prefix, dtype, device)
         p = params
         self.hidden, self.heads = int(p["hidden"]), int(p["heads"])
-        self.describe_key = f"latent_attention/{self.heads}"     # layers with as many heads share a step's description
         self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
         self.kv_rank, self.q_rank = int(p["kv_rank"]), int(p["q_rank"])
         self.scale, self.eps = float(p["scale"]), float(p["eps"])
+        # layers of the same sizes share a step's description
+        self.describe_key = f"latent_attention/{self.heads}/{self.dim}/{self.vdim}/{self.kv_rank}"
+        self.ukv: Linear = None             # [uk; uv] stacked, for steps that form keys and values
         if not 1 <= self.kv_rank <= 1024:
             raise ValueError(f"kv_rank {self.kv_rank} is outside 1..1024")
         self.down: Linear = None            # [dq; dkv; g]
@@ -93,23 +115,66 @@ class LatentAttention(Part):
         self.wq = tensors.pop(n("dq.norm")).to(torch.float32).contiguous()
         self.wkv = tensors.pop(n("dkv.norm")).to(torch.float32).contiguous()
         self.uq = Linear(tensors.pop(n("uq")))
-        self.uk_t = tensors.pop(n("uk")).view(self.heads, self.dim, self.kv_rank).transpose(1, 2).contiguous()
-        self.uv = tensors.pop(n("uv")).view(self.heads, self.vdim, self.kv_rank).contiguous()
+        self.uk_t = tensors[n("uk")].view(self.heads, self.dim, self.kv_rank).transpose(1, 2).contiguous()
+        uk, uv = tensors[n("uk")], tensors.pop(n("uv"))
+        if self._prompt_by_heads(uk.dtype):
+            self.ukv = Linear(torch.cat([uk, uv], dim=0))
+        del tensors[n("uk")]
+        self.uv = uv.view(self.heads, self.vdim, self.kv_rank).contiguous()
         self.o = Linear(tensors.pop(n("o")))
 
+    def _prompt_by_heads(self, weight_dtype=None) -> bool:
+        """Whether prompt portions are attended per head: bfloat16 and heads
+        of the size the tcgen05 prompt kernel takes.  A portion's queries then
+        meet keys and values ``k_h = Uk_h c``, ``v_h = Uv_h c`` that the step
+        forms from the cached latents of the portion's whole context (one
+        product over the gathered latents), which costs ``dim + vdim`` instead
+        of ``2 kv_rank`` multiplications per query, key and head.  Single
+        tokens stay with the latents, which all their heads share."""
+        dtype = weight_dtype if weight_dtype is not None else self.dtype
+        return (dtype == torch.bfloat16 and self.dtype == torch.bfloat16 and torch.device(self.device).type == "cuda"
+                and self.dim == self.vdim == ops.UMMA_ATTENTION_HEAD_DIM and self.kv_rank % 8 == 0)
+
     def describe_step(self, layout, put) -> LatentStep:
+        r = layout.n_entries
+        q_len = [int(n) for n in layout.q_len[:r]]
         tile_entry, tile_q0 = [], []
-        for i in range(layout.n_entries):
-            for q0 in range(0, int(layout.q_len[i]), QUERY_TILE):
+        for i in range(r):
+            for q0 in range(0, q_len[i], QUERY_TILE):
                 tile_entry.append(i), tile_q0.append(q0)
+        prompt = None
+        portions = [i for i in range(r) if q_len[i] > 1]
+        if portions and self.ukv is not None:
+            g_entry, g_pos, tabs, at = [], [], [[] for _ in range(r)], 0
+            for i in portions:
+                total = int(layout.ctx_start[i]) + q_len[i]
+                pages = (total + PROMPT_PAGE - 1) // PROMPT_PAGE
+                g_entry += [i] * (pages * PROMPT_PAGE)
+                g_pos += list(range(total)) + [0] * (pages * PROMPT_PAGE - total)      # padding repeats position 0; it is never visible
+                tabs[i] = list(range(at, at + pages))
+                at += pages
+            width = max(len(t) for t in tabs)
+            table = [t + [-1] * (width - len(t)) for t in tabs]
+            full = ops.UMMA_ATTENTION_TILE
+            blocks = sum((q_len[i] + full - 1) // full for i in portions) * self.heads
+            rows = full // 2 if 2 * blocks <= ops.sm_count(self.device) else full
+            p_entry, p_q0 = [], []
+            for i in portions:
+                for q0 in range(0, q_len[i], rows):
+                    p_entry.append(i), p_q0.append(q0)
+            prompt = PromptStep(put(g_entry), put(g_pos), len(g_entry), put([v for t in table for v in t]).view(r, width),
+                                put(p_entry), put(p_q0), len(p_entry), rows,
+                                max(int(layout.ctx_start[i]) + q_len[i] for i in portions),
+                                put([i for i in range(r) for _ in range(q_len[i])]))
+        # tiles of (token, head) rows over the latents: every entry, or only the single tokens beside such portions
         small, large = ops.LATENT_MMA_TILES
-        rows = [int(n) * self.heads for n in layout.q_len[:layout.n_entries]]
+        rows = [(0 if prompt is not None and n > 1 else n * self.heads) for n in q_len]
         bm = small if max(rows) <= small else large
         row_entry, row0 = [], []
         for i, n in enumerate(rows):
-            for r in range(0, n, bm):
-                row_entry.append(i), row0.append(r)
-        return LatentStep(put(tile_entry), put(tile_q0), len(tile_entry), bm, put(row_entry), put(row0), len(row_entry))
+            for r0 in range(0, n, bm):
+                row_entry.append(i), row0.append(r0)
+        return LatentStep(put(tile_entry), put(tile_q0), len(tile_entry), bm, put(row_entry), put(row0), len(row_entry), prompt)
 
     def _per_head(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """x ``[N, heads, a]`` (a view), w ``[heads, b, a]`` -> float32 ``[N, heads, b]``
@@ -137,8 +202,16 @@ class LatentAttention(Part):
         ops.latent_prep(p, self.wq, self.wkv, self.eps, self.q_rank, self.kv_rank, self.heads, cq, cache, page_stride,
                         ctx.page_size, ctx.slot_maps[g], gate)
         q = self.uq.forward(cq, out_dtype=x.dtype).view(n, self.heads, self.dim)
+        if out is None:
+            out = torch.empty((n, self.heads * self.vdim), dtype=x.dtype, device=x.device)
+        prompt = step.prompt
+        if prompt is not None:
+            self._attend_portions(q, gate, out, ctx, prompt, cache, page_stride, g)
+            if not step.n_row_tiles:
+                return out
         q_lat = self._per_head(q, self.uk_t)                                   # float32 [N, heads, kv_rank]
-        o_lat = torch.empty((self.heads, n, self.kv_rank), dtype=x.dtype, device=x.device).transpose(0, 1)
+        alloc = torch.zeros if prompt is not None else torch.empty             # rows of portions stay unwritten, and finite
+        o_lat = alloc((self.heads, n, self.kv_rank), dtype=x.dtype, device=x.device).transpose(0, 1)
         if ops.attn_latent_mma_ok(self.kv_rank, cache):
             splits = ops.attn_latent_mma_splits(step.n_row_tiles, step.bm, self.kv_rank, ctx.max_ctx_len)
             ops.attn_latent_mma(q_lat, o_lat, cache, page_stride, ctx.page_size, ctx.block_tables[g], step.row_tile_entry,
@@ -149,9 +222,27 @@ class LatentAttention(Part):
                                   step.tile_q0, step.n_tiles, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start,
                                   self.scale)
         heads = self._per_head(o_lat, self.uv)                                 # float32 [N, heads, vdim]
-        if out is None:
-            out = torch.empty((n, self.heads * self.vdim), dtype=x.dtype, device=x.device)
+        if prompt is not None:                                                 # only the single tokens' rows
+            return ops.gate_heads(heads, gate, out, prompt.row_entry, ctx.entry_q_len, prompt_rows=False)
         return ops.gate_heads(heads, gate, out)
+
+    def _attend_portions(self, q, gate, out, ctx, prompt: "PromptStep", cache, page_stride, g) -> None:
+        """The step's prompt portions per head: expand the cached latents of
+        their contexts into keys and values, laid out in pages of their own,
+        and run the tensor-core prompt kernel over them; gated rows into out."""
+        n, h, d = q.shape[0], self.heads, self.dim
+        lat = torch.empty((prompt.n_gather, self.kv_rank), dtype=cache.dtype, device=q.device)
+        ops.gather_latents(cache, page_stride, ctx.page_size, ctx.block_tables[g], prompt.g_entry, prompt.g_pos, lat)
+        kv = self.ukv.forward(lat, out_dtype=cache.dtype)                      # [G, (k | v) x heads x d]
+        pages = prompt.n_gather // PROMPT_PAGE
+        pool = kv.view(pages, PROMPT_PAGE, 2, h, d).permute(0, 2, 3, 1, 4).contiguous()     # [page][k|v][head][slot][d]
+        attn = torch.empty((n, h * d), dtype=q.dtype, device=q.device)
+        splits = ops.attn_prefill_umma_splits(prompt.n_tiles, h, prompt.max_keys)
+        ops.attn_prefill_umma(q.view(n, h * d), h * d, attn, pool[0, 0], pool[0, 1], pool.stride(0), PROMPT_PAGE,
+                              prompt.block_tables, prompt.tile_entry, prompt.tile_q0, prompt.n_tiles, ctx.entry_q_start,
+                              ctx.entry_q_len, ctx.entry_ctx_start, h, h, d, self.scale, 0, splits,
+                              tile_rows=prompt.tile_rows)
+        ops.gate_heads(attn.view(n, h, d), gate, out, prompt.row_entry, ctx.entry_q_len, prompt_rows=True)
 
     @property
     def inner_width(self) -> int:

@@ -142,7 +142,11 @@ KX_B = dict(architecture="Kunonex", width=96, vocab=411, norm=dict(eps=3e-6), lo
 KX_C = dict(architecture="Kunonex", width=40, vocab=97, norm=dict(eps=1e-6), logit_scale=1.0,
             layers=[_kx_attn(2, 8, 12, 16, 16, 0.7, ff=64), _kx_gru(24), _kx_attn(4, 12, 4, 33, 28, 0.4, ff=48)], loop=None)
 KX_D = dict(KX_C, loop=dict(start=2, stop=3, times=1), logit_scale=2.0)
-KX = {"A": KX_A, "B": KX_B, "C": KX_C, "D": KX_D}
+# heads of 128: in bfloat16 prompt portions are attended per head by the tcgen05 prompt kernel, single tokens over the latents
+KX_E = dict(architecture="Kunonex", width=128, vocab=200, norm=dict(eps=1e-6), logit_scale=0.7,
+            layers=[_kx_attn(2, 128, 128, 48, 64, 0.09, ff=160), _kx_gru(128, ff=96), _kx_attn(3, 128, 128, 64, 40, 0.09)],
+            loop=dict(start=0, stop=1, times=2))
+KX = {"A": KX_A, "B": KX_B, "C": KX_C, "D": KX_D, "E": KX_E}
 
 
 def kunonex_tensors(cfg: dict, seed: int, sharpen: float = 6.0, lively: float = 12.0):

@@ -315,7 +315,7 @@ def _logits_in_steps(runner, rid, toks, sizes):
 
 @gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_model_whole_one_by_one_and_in_portions(dtype, name):
     """Every layer's residual stream is not compared here; the logits at every position are, for three ways
     of cutting the same prompt.  In float32 the three agree with each other almost to the bit."""
@@ -325,6 +325,9 @@ def test_model_whole_one_by_one_and_in_portions(dtype, name):
     want = plain.forward(cfg, w, toks)
     whole = _logits_in_steps(runner, "w", toks, [150])
     assert _rel(whole, want) < PTOL[dtype]
+    if name == "E":
+        mixer = model.blocks[0].mixer
+        assert (mixer.ukv is not None) == (dtype == torch.bfloat16)    # bfloat16: portions go per head
     ones = _logits_in_steps(runner, "o", toks[:70], [1])              # the captured decode graph after three steps
     assert runner.graph_replays > 0 and _rel(ones, want[:70]) < PTOL[dtype]
     cut = _logits_in_steps(runner, "c", toks, [2, 3, 17, 1, 16, 5, 32, 2, 15, 64, 2])
@@ -336,11 +339,12 @@ def test_model_whole_one_by_one_and_in_portions(dtype, name):
 
 @gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_batches_of_unequal_requests_and_reused_slots(dtype):
+@pytest.mark.parametrize("name", ["A", "E"])
+def test_batches_of_unequal_requests_and_reused_slots(dtype, name):
     """Four requests of unequal length, portions beside single tokens, against each alone; then four more
     in the slots and pages the first ones gave back."""
     from inferflux_b200.engine import StepEntry
-    cfg = KX["A"]
+    cfg = KX[name]
     model, runner, w = _runner_for(cfg, dtype, 41, tokens=4 * 128)
     rng = random.Random(3)
     for round_ in range(2):
