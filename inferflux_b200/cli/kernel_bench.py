@@ -271,7 +271,7 @@ class Case:
                 state, args_ = torch.zeros(1, h, device=DEV), (it([0] * n_seg), it([k * seg for k in range(n_seg)]), n_seg, it([0]),
                                                                  it([0]), it([rows]), it([0]), 1, True)
             self.n_rot, self.bytes = 1, rows * h * (12 + 2) + (rows * h * 8 if rows > 64 else 0)
-            self.run = lambda i: ops.mingru_scan(proj, state, o, *args_)
+            self.run = lambda i: ops.mingru_scan(proj, None, state, o, *args_)
         elif name == "latent_prep":
             kvr, qr = LATENT
             ps = PAGE_SIZE

@@ -222,7 +222,7 @@ namespace {
 // one (prompt == 0) and leaves the others as they are.
 template <typename TI, typename TO>
 __global__ void gate_heads_kernel(const TI* __restrict__ in, HeadLayout il, const float* __restrict__ gate,
-                                  TO* __restrict__ out, int n_heads, int width, const int* __restrict__ row_entry,
+                                  TO* __restrict__ out, long long out_stride, int n_heads, int width, const int* __restrict__ row_entry,
                                   const int* __restrict__ entry_q_len, int prompt) {
   pdl_enter();
   const int row = blockIdx.x;
@@ -230,7 +230,7 @@ __global__ void gate_heads_kernel(const TI* __restrict__ in, HeadLayout il, cons
   const int total = n_heads * width;
   for (int i = threadIdx.x; i < total; i += blockDim.x) {
     const int h = i / width, d = i - h * width;
-    out[(size_t)row * total + i] = Num<TO>::from_f(Num<TI>::to_f(in[(size_t)row * il.row + (size_t)h * il.head + d]) * gate[(size_t)row * n_heads + h]);
+    out[(size_t)row * out_stride + i] = Num<TO>::from_f(Num<TI>::to_f(in[(size_t)row * il.row + (size_t)h * il.head + d]) * gate[(size_t)row * n_heads + h]);
   }
 }
 
@@ -251,7 +251,7 @@ __global__ void gather_latents_kernel(const T* __restrict__ cache, long long pag
 
 // in_dtype / out_dtype: IFX_F32 or IFX_BF16.  row_entry (with entry_q_len) may be null: every row is taken.
 IFX_API int ifx_gate_heads(const void* in, int in_dtype, long long in_row, long long in_head, const float* gate, void* out,
-                           int out_dtype, int n_rows, int n_heads, int width, const int* row_entry,
+                           long long out_stride, int out_dtype, int n_rows, int n_heads, int width, const int* row_entry,
                            const int* entry_q_len, int prompt, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   const int total = n_heads * width;
@@ -259,7 +259,7 @@ IFX_API int ifx_gate_heads(const void* in, int in_dtype, long long in_row, long 
   HeadLayout il{in_row, in_head};
   int rc;
 #define IFX_GH(TI, TO) rc = launch_pdl(gate_heads_kernel<TI, TO>, dim3(n_rows), dim3(threads), 0, stream, (const TI*)in, il, gate, \
-                                       (TO*)out, n_heads, width, row_entry, entry_q_len, prompt)
+                                       (TO*)out, out_stride, n_heads, width, row_entry, entry_q_len, prompt)
   if (in_dtype == IFX_F32 && out_dtype == IFX_F32) IFX_GH(float, float);
   else if (in_dtype == IFX_F32 && out_dtype == IFX_BF16) IFX_GH(float, bf16);
   else if (in_dtype == IFX_BF16 && out_dtype == IFX_BF16) IFX_GH(bf16, bf16);

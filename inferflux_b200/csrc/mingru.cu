@@ -22,6 +22,7 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf
 
 struct GruStep {
   const float* proj;          // [N, 3 * width]
+  const float* bias;          // [2 * width]: the biases of z and of x, or null
   const int* seg_entry;       // [segments]
   const int* seg_t0;          // [segments] first token of the segment within its entry
   const int* entry_q_start;   // [entries]
@@ -30,9 +31,9 @@ struct GruStep {
   int width;
 };
 
-__device__ __forceinline__ void gate(const float* row, int width, int ch, float& a, float& b) {
-  const float z = sigmoid_f(row[ch]);
-  const float u = row[width + ch];
+__device__ __forceinline__ void gate(const float* row, int width, int ch, float bz, float bx, float& a, float& b) {
+  const float z = sigmoid_f(row[ch] + bz);
+  const float u = row[width + ch] + bx;
   const float c = u >= 0.0f ? u + 0.5f : sigmoid_f(u);
   a = 1.0f - z;
   b = z * c;
@@ -46,11 +47,12 @@ mingru_segment_sums_kernel(GruStep s, float* __restrict__ seg_a, float* __restri
   const int e = s.seg_entry[seg], t0 = s.seg_t0[seg];
   const int n = min(IFX_MINGRU_SEGMENT, s.entry_q_len[e] - t0);
   const float* row = s.proj + (size_t)(s.entry_q_start[e] + t0) * 3 * s.width;
+  const float bz = s.bias ? s.bias[ch] : 0.0f, bx = s.bias ? s.bias[s.width + ch] : 0.0f;
   float A = 1.0f, B = 0.0f;
 #pragma unroll 8
   for (int t = 0; t < n; ++t, row += 3 * s.width) {
     float a, b;
-    gate(row, s.width, ch, a, b);
+    gate(row, s.width, ch, bz, bx, a, b);
     A *= a;
     B = fmaf(a, B, b);
   }
@@ -76,7 +78,8 @@ mingru_carry_kernel(GruStep s, const int* __restrict__ entry_first_seg, const fl
 
 template <typename TO>
 __global__ void __launch_bounds__(128)
-mingru_scan_kernel(GruStep s, const float* __restrict__ seg_start, float* __restrict__ state, TO* __restrict__ out) {
+mingru_scan_kernel(GruStep s, const float* __restrict__ seg_start, float* __restrict__ state, TO* __restrict__ out,
+                   long long out_stride) {
   pdl_enter();
   const int seg = blockIdx.x, ch = blockIdx.y * blockDim.x + threadIdx.x;
   if (ch >= s.width) return;
@@ -85,13 +88,14 @@ mingru_scan_kernel(GruStep s, const float* __restrict__ seg_start, float* __rest
   const int n = min(IFX_MINGRU_SEGMENT, len - t0);
   const size_t row0 = (size_t)(s.entry_q_start[e] + t0);
   const float* row = s.proj + row0 * 3 * s.width;
-  TO* o = out + row0 * s.width + ch;
+  TO* o = out + row0 * out_stride + ch;
   float* st = state + (size_t)s.entry_slot[e] * s.width + ch;
+  const float bz = s.bias ? s.bias[ch] : 0.0f, bx = s.bias ? s.bias[s.width + ch] : 0.0f;
   float S = seg_start ? seg_start[(size_t)seg * s.width + ch] : *st;
 #pragma unroll 8
-  for (int t = 0; t < n; ++t, row += 3 * s.width, o += s.width) {
+  for (int t = 0; t < n; ++t, row += 3 * s.width, o += out_stride) {
     float a, b;
-    gate(row, s.width, ch, a, b);
+    gate(row, s.width, ch, bz, bx, a, b);
     S = fmaf(a, S, b);
     const float g = row[2 * s.width + ch];
     *o = Num<TO>::from_f(S * (g * sigmoid_f(g)));
@@ -102,15 +106,16 @@ mingru_scan_kernel(GruStep s, const float* __restrict__ seg_start, float* __rest
 
 IFX_API int ifx_mingru_segment() { return IFX_MINGRU_SEGMENT; }
 
-// proj float32 [N, 3 * width]; state float32 [slots, width]; out [N, width] of out_dtype.  The segments of the
+// proj float32 [N, 3 * width]; bias float32 [2 * width] (of z and x) or null; state float32 [slots, width]; out
+// [N, width] of out_dtype, rows out_stride elements apart.  The segments of the
 // step are listed by seg_entry / seg_t0 (an entry's segments in order, entry_first_seg[e] the index of its
 // first).  multi != 0: some entry has more than one segment, and scratch holds 3 * n_segments * width floats.
-IFX_API int ifx_mingru_scan(const float* proj, float* state, void* out, int out_dtype, const int* seg_entry,
+IFX_API int ifx_mingru_scan(const float* proj, const float* bias, float* state, void* out, long long out_stride, int out_dtype, const int* seg_entry,
                             const int* seg_t0, int n_segments, const int* entry_first_seg, const int* entry_q_start,
                             const int* entry_q_len, const int* entry_slot, int n_entries, int width, int multi,
                             float* scratch, cudaStream_t stream) {
   if (n_segments <= 0 || width <= 0) return 0;
-  GruStep s{proj, seg_entry, seg_t0, entry_q_start, entry_q_len, entry_slot, width};
+  GruStep s{proj, bias, seg_entry, seg_t0, entry_q_start, entry_q_len, entry_slot, width};
   const int threads = 128, cols = (width + threads - 1) / threads;
   if (cols > 65535) return IFX_ERR_UNSUPPORTED;
   int rc;
@@ -128,10 +133,10 @@ IFX_API int ifx_mingru_scan(const float* proj, float* state, void* out, int out_
   }
   if (out_dtype == IFX_F32)
     rc = launch_pdl(mingru_scan_kernel<float>, dim3(n_segments, cols), dim3(threads), 0, stream, s, (const float*)seg_start,
-                    state, (float*)out);
+                    state, (float*)out, out_stride);
   else if (out_dtype == IFX_BF16)
     rc = launch_pdl(mingru_scan_kernel<bf16>, dim3(n_segments, cols), dim3(threads), 0, stream, s, (const float*)seg_start,
-                    state, (bf16*)out);
+                    state, (bf16*)out, out_stride);
   else
     return IFX_ERR_UNSUPPORTED;
   return rc ? rc : IFX_LAUNCH_CHECK();

@@ -7,7 +7,7 @@
 namespace {
 template <typename TO>
 __global__ void polynorm_kernel(const float* __restrict__ z, long long z_stride, const float* __restrict__ bias,
-                                const float* __restrict__ coeff, float eps, TO* __restrict__ out, int n) {
+                                const float* __restrict__ coeff, float eps, TO* __restrict__ out, long long out_stride, int n) {
   pdl_enter();
   extern __shared__ float row_buf[];
   __shared__ float red[32];
@@ -28,7 +28,7 @@ __global__ void polynorm_kernel(const float* __restrict__ z, long long z_stride,
   const float r2 = coeff[1] / sqrtf(s2 / (float)n + eps);
   const float r3 = coeff[2] / sqrtf(s3 / (float)n + eps);
   const float e = coeff[3];
-  TO* o = out + (size_t)blockIdx.x * n;
+  TO* o = out + (size_t)blockIdx.x * out_stride;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const float v = row_buf[i];
     const float v2 = v * v;
@@ -39,7 +39,7 @@ __global__ void polynorm_kernel(const float* __restrict__ z, long long z_stride,
 // The same with 16-byte loads and 8-byte stores: n a multiple of 4, rows and bias on 16-byte boundaries.
 template <typename TO>
 __global__ void polynorm_vec_kernel(const float* __restrict__ z, long long z_stride, const float* __restrict__ bias,
-                                    const float* __restrict__ coeff, float eps, TO* __restrict__ out, int n) {
+                                    const float* __restrict__ coeff, float eps, TO* __restrict__ out, long long out_stride, int n) {
   pdl_enter();
   extern __shared__ float4 row_buf4[];
   __shared__ float red[32];
@@ -67,7 +67,7 @@ __global__ void polynorm_vec_kernel(const float* __restrict__ z, long long z_str
   const float r2 = coeff[1] / sqrtf(s2 / (float)n + eps);
   const float r3 = coeff[2] / sqrtf(s3 / (float)n + eps);
   const float e0 = coeff[3];
-  TO* o = out + (size_t)blockIdx.x * n;
+  TO* o = out + (size_t)blockIdx.x * out_stride;
   for (int i = threadIdx.x; i < groups; i += blockDim.x) {
     const float4 v = row_buf4[i];
     float y[4];
@@ -92,14 +92,14 @@ __global__ void polynorm_vec_kernel(const float* __restrict__ z, long long z_str
 
 // z float32 [rows, n] (row stride z_stride), bias float32 [n] or null, coeff float32 [4] = a, b, c, e.
 IFX_API int ifx_polynorm(const float* z, long long z_stride, const float* bias, const float* coeff, float eps, void* out,
-                         int out_dtype, int n_rows, int n, cudaStream_t stream) {
+                         long long out_stride, int out_dtype, int n_rows, int n, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   const size_t smem = (size_t)n * sizeof(float);
   if (smem > 200 * 1024) return IFX_ERR_UNSUPPORTED;
   int threads = 64;
   while (threads < 1024 && threads * 4 < n) threads <<= 1;
   int rc;
-  const bool vec = n % 4 == 0 && (z_stride & 3) == 0 && (((uintptr_t)z | (uintptr_t)bias | (uintptr_t)out) & 15) == 0;
+  const bool vec = n % 4 == 0 && (z_stride & 3) == 0 && (out_stride & 3) == 0 && (((uintptr_t)z | (uintptr_t)bias | (uintptr_t)out) & 15) == 0;
   if (vec && (out_dtype == IFX_F32 || out_dtype == IFX_BF16)) {
     threads = 64;
     while (threads < 1024 && threads * 8 < n) threads <<= 1;
@@ -107,12 +107,12 @@ IFX_API int ifx_polynorm(const float* z, long long z_stride, const float* bias, 
       auto kern = polynorm_vec_kernel<float>;
       if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return (int)cudaGetLastError();
-      rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, z, z_stride, bias, coeff, eps, (float*)out, n);
+      rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, z, z_stride, bias, coeff, eps, (float*)out, out_stride, n);
     } else {
       auto kern = polynorm_vec_kernel<bf16>;
       if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return (int)cudaGetLastError();
-      rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, z, z_stride, bias, coeff, eps, (bf16*)out, n);
+      rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, z, z_stride, bias, coeff, eps, (bf16*)out, out_stride, n);
     }
     return rc ? rc : IFX_LAUNCH_CHECK();
   }
@@ -120,12 +120,12 @@ IFX_API int ifx_polynorm(const float* z, long long z_stride, const float* bias, 
     auto kern = polynorm_kernel<float>;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return (int)cudaGetLastError();
-    rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, z, z_stride, bias, coeff, eps, (float*)out, n);
+    rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, z, z_stride, bias, coeff, eps, (float*)out, out_stride, n);
   } else if (out_dtype == IFX_BF16) {
     auto kern = polynorm_kernel<bf16>;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return (int)cudaGetLastError();
-    rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, z, z_stride, bias, coeff, eps, (bf16*)out, n);
+    rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, z, z_stride, bias, coeff, eps, (bf16*)out, out_stride, n);
   } else {
     return IFX_ERR_UNSUPPORTED;
   }

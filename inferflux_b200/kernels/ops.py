@@ -115,10 +115,10 @@ def _lib():
                                         c_int, c_int, c_int, c_void_p]
         lib.ifx_embed_sinusoid_layernorm.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_double,
                                                      c_void_p, c_int, c_int, c_int, c_void_p]
-        lib.ifx_polynorm.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_polynorm.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_float, c_void_p, c_ll, c_int, c_int, c_int, c_void_p]
         lib.ifx_mingru_segment.argtypes = []
-        lib.ifx_mingru_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                        c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+        lib.ifx_mingru_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
         lib.ifx_latent_prep.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p,
                                         c_void_p, c_int, c_ll, c_int, c_void_p, c_void_p, c_int, c_void_p]
         lib.ifx_attn_latent_paged.argtypes = [c_void_p, c_ll, c_ll, c_void_p, c_ll, c_ll, c_void_p, c_int, c_ll, c_int,
@@ -131,7 +131,7 @@ def _lib():
         lib.ifx_attn_latent_mma_max_rank.argtypes = []
         lib.ifx_add_into.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_void_p]
         lib.ifx_add_rows_vector.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
-        lib.ifx_gate_heads.argtypes = [c_void_p, c_int, c_ll, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+        lib.ifx_gate_heads.argtypes = [c_void_p, c_int, c_ll, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p,
                                        c_void_p, c_int, c_void_p]
         lib.ifx_gather_latents.argtypes = [c_void_p, c_int, c_ll, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                            c_int, c_void_p]
@@ -923,8 +923,8 @@ def polynorm(z: torch.Tensor, bias: Optional[torch.Tensor], coeff: torch.Tensor,
     _need(coeff.dtype == torch.float32 and coeff.numel() == 4, "polynorm: four float32 coefficients")
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == f, "polynorm: bias float32 [F]")
-    _need(out.is_contiguous() and tuple(out.shape) == (m, f), "polynorm: out [M, F]")
-    _check(_lib().ifx_polynorm(_ptr(z), z.stride(0), _ptr(bias), _ptr(coeff), float(eps), _ptr(out), _code(out), m, f,
+    _need(out.stride(1) == 1 and tuple(out.shape) == (m, f), "polynorm: out [M, F] with unit inner stride")
+    _check(_lib().ifx_polynorm(_ptr(z), z.stride(0), _ptr(bias), _ptr(coeff), float(eps), _ptr(out), out.stride(0), _code(out), m, f,
                                _stream()), "polynorm")
     return out
 
@@ -934,11 +934,12 @@ def mingru_segment() -> int:
     return int(_lib().ifx_mingru_segment())
 
 
-def mingru_scan(proj: torch.Tensor, state: torch.Tensor, out: torch.Tensor, seg_entry: torch.Tensor, seg_t0: torch.Tensor,
+def mingru_scan(proj: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, out: torch.Tensor, seg_entry: torch.Tensor, seg_t0: torch.Tensor,
                 n_segments: int, entry_first_seg: torch.Tensor, entry_q_start: torch.Tensor, entry_q_len: torch.Tensor,
                 entry_slot: torch.Tensor, n_entries: int, multi: bool) -> torch.Tensor:
     """The minGRU recurrence over a step: proj float32 [N, 3W] = the stacked
-    projections [z | x | g] of every token, state float32 [slots, W] (read at
+    projections [z | x | g] of every token (bias float32 [2W]: the biases of z
+    and x, added here), state float32 [slots, W] (read at
     an entry's first token, written after its last), out [N, W] =
     S_t * silu(g_t)."""
     n, w3 = proj.shape
@@ -946,11 +947,13 @@ def mingru_scan(proj: torch.Tensor, state: torch.Tensor, out: torch.Tensor, seg_
     _need(proj.dtype == torch.float32 and proj.is_contiguous() and w3 == 3 * width, "mingru_scan: proj float32 [N, 3W]")
     _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == width,
           "mingru_scan: state float32 [slots, W]")
-    _need(out.is_contiguous() and tuple(out.shape) == (n, width), "mingru_scan: out [N, W]")
+    _need(out.stride(1) == 1 and tuple(out.shape) == (n, width), "mingru_scan: out [N, W] with unit inner stride")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == 2 * width, "mingru_scan: bias float32 [2W]")
     for t in (seg_entry, seg_t0, entry_first_seg, entry_q_start, entry_q_len, entry_slot):
         _need(t.dtype == torch.int32, "mingru_scan: int32 metadata")
     scratch = torch.empty(3 * n_segments * width, dtype=torch.float32, device=proj.device) if multi else None
-    _check(_lib().ifx_mingru_scan(_ptr(proj), _ptr(state), _ptr(out), _code(out), _ptr(seg_entry), _ptr(seg_t0), n_segments,
+    _check(_lib().ifx_mingru_scan(_ptr(proj), _ptr(bias), _ptr(state), _ptr(out), out.stride(0), _code(out), _ptr(seg_entry), _ptr(seg_t0), n_segments,
                                   _ptr(entry_first_seg), _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_slot),
                                   n_entries, width, 1 if multi else 0, _ptr(scratch), _stream()), "mingru_scan")
     return out
@@ -1019,9 +1022,9 @@ def gate_heads(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, row_entry
     n, n_heads, width = x.shape
     _need(gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (n, n_heads),
           "gate_heads: gate float32 [N, heads]")
-    _need(out.is_contiguous() and tuple(out.shape) == (n, n_heads * width), "gate_heads: out [N, heads * width]")
+    _need(out.stride(1) == 1 and tuple(out.shape) == (n, n_heads * width), "gate_heads: out [N, heads * width], unit inner stride")
     row, head = _head_layout(x, n_heads, width, "gate_heads x")
-    _check(_lib().ifx_gate_heads(_ptr(x), _code(x), row, head, _ptr(gate), _ptr(out), _code(out), n, n_heads, width,
+    _check(_lib().ifx_gate_heads(_ptr(x), _code(x), row, head, _ptr(gate), _ptr(out), out.stride(0), _code(out), n, n_heads, width,
                                  _ptr(row_entry), _ptr(entry_q_len), 1 if prompt_rows else 0, _stream()), "gate_heads")
     return out
 

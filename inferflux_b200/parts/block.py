@@ -72,7 +72,7 @@ class ParallelBlock:
     family = "arrangement"
     roles = {"norm": "norm", "shift": "shift", "mixer": "mixer", "feed_forward": "feed_forward"}
     optional_roles = frozenset({"shift", "feed_forward"})
-    JOINT_OUTPUT = False
+    JOINT_OUTPUT = True
     FUSED_SINGLE = True
 
     def __init__(self, parts: Dict[str, object], position_name: Optional[str]):

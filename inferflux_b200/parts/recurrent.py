@@ -66,9 +66,8 @@ class MinGRU(Part):
         mats = [tensors.pop(n(x)) for x in ("z", "x", "g")]
         if len({m.dtype for m in mats}) > 1:
             mats = [m.float() for m in mats]
-        bias = torch.cat([tensors.pop(n("z.b")).float(), tensors.pop(n("x.b")).float(),
-                          torch.zeros(self.width, dtype=torch.float32, device=mats[0].device)])
-        self.zxg = Linear(torch.cat(mats, dim=0), bias)
+        self.bias = torch.cat([tensors.pop(n("z.b")).float(), tensors.pop(n("x.b")).float()]).contiguous()   # added by the scan
+        self.zxg = Linear(torch.cat(mats, dim=0))
         del mats
         self.o = Linear(tensors.pop(n("o")))
 
@@ -87,7 +86,7 @@ class MinGRU(Part):
         proj = self.zxg.forward(x, out_dtype=torch.float32)
         if out is None:
             out = torch.empty((x.shape[0], self.width), dtype=x.dtype, device=x.device)
-        return ops.mingru_scan(proj, run.states["gru"], out, step.seg_entry, step.seg_t0, step.n_segments,
+        return ops.mingru_scan(proj, self.bias, run.states["gru"], out, step.seg_entry, step.seg_t0, step.n_segments,
                                step.entry_first_seg, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_slot, ctx.n_entries,
                                step.multi)
 
