@@ -296,7 +296,7 @@ class Case:
             q = torch.randn(nh, n, kvr, device=DEV).transpose(0, 1)
             out = torch.empty(nh, n, kvr, **bf).transpose(0, 1)
             qs, ql, cs = it([i * q_len for i in range(b)]), it([q_len] * b), it([ctx - q_len] * b)
-            bm = 16 if q_len * nh <= 16 else 64
+            bm = next((t for t in ops.LATENT_MMA_TILES if q_len * nh <= t), 64)
             tiles = [(e, r) for e in range(b) for r in range(0, q_len * nh, bm)]
             te, tr = it([t[0] for t in tiles]), it([t[1] for t in tiles])
             splits = ops.attn_latent_mma_splits(len(tiles), bm, kvr, ctx)

@@ -67,14 +67,19 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
                        LatentTiles b, int n_heads, int rank, float scale, int n_splits,
                        float* __restrict__ part_o, float* __restrict__ part_ml) {
   constexpr int BM = 16 * MT, RP = 64 * RT, LD = RP + PAD, LDP = BN + PAD, LDS = BN + 4;
-  constexpr int NT_S = MT;                 // key tiles of 8 per warp in S: 8 warps cover MT x 8 (row tile, key tile) pairs
+  // S is shared out over the 8 warps in one of two ways.  By keys (NP == 1): a warp takes one row tile and MT of the 8
+  // key tiles over all of R.  By R (NP > 1, taken for the low tiles of decode steps where the sums over R would
+  // otherwise be one long chain of dependent products): a warp takes one row tile, all 8 key tiles and 1/NP of R,
+  // and the NP partial scores are added when the softmax reads them.
+  constexpr int NP = (MT <= 2 && RT >= 2) ? 8 / MT : 1;
+  constexpr int NT_S = NP > 1 ? 8 : MT;
   pdl_enter();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);                    // [BM][LD]
   bf16* cs = qs + BM * LD;                                          // [2][BN][LD]
   bf16* ps = cs + 2 * BN * LD;                                      // [BM][LDP]
-  float* ss = reinterpret_cast<float*>(ps + BM * LDP);              // [BM][LDS]
-  float* row_m = ss + BM * LDS;                                     // [BM]
+  float* ss = reinterpret_cast<float*>(ps + BM * LDP);              // [NP][BM][LDS]
+  float* row_m = ss + NP * BM * LDS;                                // [BM]
   float* row_l = row_m + BM;
   float* row_a = row_l + BM;
   int* row_pos = reinterpret_cast<int*>(row_a + BM);                // [BM] position of each row's token, -1 = no such row
@@ -136,7 +141,10 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
 #pragma unroll
     for (int n = 0; n < RT; ++n) { o[m][n][0] = o[m][n][1] = o[m][n][2] = o[m][n][3] = 0.0f; }
 
-  const int sm = warp % MT, sg = warp / MT;                         // this warp's row tile and key group in S
+  const int sm = warp % MT;                                         // this warp's row tile in S
+  const int sg = NP > 1 ? 0 : warp / MT;                            // its group of key tiles (by keys)
+  const int sp = NP > 1 ? warp / MT : 0;                            // its part of R (by R)
+  constexpr int KSTEPS = RP / 16 / NP;                              // steps of 16 columns this warp sums over
   if (kt_lo < kt_hi) load_tile(kt_lo, 0);
   cp_async_commit();
   for (int kt = kt_lo; kt < kt_hi; ++kt) {
@@ -152,16 +160,16 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
     for (int j = 0; j < NT_S; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
     {
       // fragments of step k + 1 are asked for before the products of step k are issued
-      const bf16* qa = qs + (sm * 16 + (lane & 15)) * LD + (lane >> 4) * 8;
-      const bf16* cb = ct + (sg * NT_S * 8 + (lane & 7)) * LD + ((lane >> 3) & 1) * 8;
+      const bf16* qa = qs + (sm * 16 + (lane & 15)) * LD + (lane >> 4) * 8 + sp * KSTEPS * 16;
+      const bf16* cb = ct + (sg * NT_S * 8 + (lane & 7)) * LD + ((lane >> 3) & 1) * 8 + sp * KSTEPS * 16;
       unsigned a[2][4], bb[2][NT_S][2];
       ldsm_x4(a[0], qa);
 #pragma unroll
       for (int j = 0; j < NT_S; ++j) ldsm_x2(bb[0][j], cb + j * 8 * LD);
 #pragma unroll 2
-      for (int k = 0; k < RP / 16; ++k) {
+      for (int k = 0; k < KSTEPS; ++k) {
         const int cur = k & 1, nxt = cur ^ 1;
-        if (k + 1 < RP / 16) {
+        if (k + 1 < KSTEPS) {
           ldsm_x4(a[nxt], qa + (k + 1) * 16);
 #pragma unroll
           for (int j = 0; j < NT_S; ++j) ldsm_x2(bb[nxt][j], cb + j * 8 * LD + (k + 1) * 16);
@@ -173,8 +181,8 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
 #pragma unroll
     for (int j = 0; j < NT_S; ++j) {
       const int col = (sg * NT_S + j) * 8 + 2 * tq;
-      float* d0 = ss + (sm * 16 + g) * LDS + col;
-      float* d1 = ss + (sm * 16 + g + 8) * LDS + col;
+      float* d0 = ss + (sp * BM + sm * 16 + g) * LDS + col;
+      float* d1 = ss + (sp * BM + sm * 16 + g + 8) * LDS + col;
       d0[0] = s[j][0]; d0[1] = s[j][1]; d1[0] = s[j][2]; d1[1] = s[j][3];
     }
     __syncthreads();
@@ -183,8 +191,15 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
       const int p = row_pos[r];                                      // -1 hides every key from a row that does not exist
       const int key = kt * BN + 2 * lane;
       const bool v0 = key <= p, v1 = key + 1 <= p;
-      const float s0 = v0 ? ss[r * LDS + 2 * lane] * scale : -INFINITY;
-      const float s1 = v1 ? ss[r * LDS + 2 * lane + 1] * scale : -INFINITY;
+      float2 sc = *reinterpret_cast<const float2*>(ss + r * LDS + 2 * lane);
+#pragma unroll
+      for (int part = 1; part < NP; ++part) {
+        const float2 more = *reinterpret_cast<const float2*>(ss + (part * BM + r) * LDS + 2 * lane);
+        sc.x += more.x;
+        sc.y += more.y;
+      }
+      const float s0 = v0 ? sc.x * scale : -INFINITY;
+      const float s1 = v1 ? sc.y * scale : -INFINITY;
       const float m_old = row_m[r];
       const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
       float p0 = 0.0f, p1 = 0.0f, alpha = 1.0f;
@@ -313,8 +328,8 @@ __global__ void attn_latent_merge_kernel(const float* __restrict__ part_o, const
 
 template <int MT, int RT>
 size_t smem_bytes() {
-  constexpr int BM = 16 * MT, LD = 64 * RT + PAD;
-  return (size_t)(BM + 2 * BN) * LD * 2 + (size_t)BM * (BN + PAD) * 2 + (size_t)BM * (BN + 4) * 4 + (size_t)4 * BM * 4;
+  constexpr int BM = 16 * MT, LD = 64 * RT + PAD, NP = (MT <= 2 && RT >= 2) ? 8 / MT : 1;
+  return (size_t)(BM + 2 * BN) * LD * 2 + (size_t)BM * (BN + PAD) * 2 + (size_t)NP * BM * (BN + 4) * 4 + (size_t)4 * BM * 4;
 }
 
 template <int MT, int RT>
@@ -351,7 +366,8 @@ IFX_API int ifx_attn_latent_mma_plan(int n_tiles, int bm, int rank, int max_keys
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int rt = (rank + 63) / 64;
-  const size_t smem = (size_t)(bm + 2 * BN) * (64 * rt + PAD) * 2 + (size_t)bm * (BN + PAD) * 2 + (size_t)bm * (BN + 4) * 4 + 4 * bm * 4;
+  const int np = (bm <= 32 && rt >= 2) ? 128 / bm : 1;
+  const size_t smem = (size_t)(bm + 2 * BN) * (64 * rt + PAD) * 2 + (size_t)bm * (BN + PAD) * 2 + (size_t)np * bm * (BN + 4) * 4 + 4 * bm * 4;
   int per_sm = (int)((size_t)(227 * 1024) / (smem + 1024));
   per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
   const int key_tiles = (max_keys + BN - 1) / BN;
@@ -384,6 +400,12 @@ IFX_API int ifx_attn_latent_mma(const float* q, long long q_row, long long q_hea
     if (rt <= 2) IFX_LM(1, 2);
     if (rt <= 4) IFX_LM(1, 4);
     IFX_LM(1, 8);
+  }
+  if (bm == 32) {
+    if (rt <= 1) IFX_LM(2, 1);
+    if (rt <= 2) IFX_LM(2, 2);
+    if (rt <= 4) IFX_LM(2, 4);
+    IFX_LM(2, 8);
   }
   if (bm == 64) {
     if (rt <= 1) IFX_LM(4, 1);

@@ -1062,7 +1062,7 @@ def add_rows_vector(a: torch.Tensor, b: torch.Tensor, v: torch.Tensor, out: torc
     return out
 
 
-LATENT_MMA_TILES = (16, 64)      # (token, head) rows per tile of the tensor-core latent attention kernel
+LATENT_MMA_TILES = (16, 32, 64)      # (token, head) rows per tile of the tensor-core latent attention kernel
 
 
 def attn_latent_mma_ok(rank: int, cache: torch.Tensor) -> bool:
@@ -1079,7 +1079,7 @@ def attn_latent_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, pag
                     entry_q_start: torch.Tensor, entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor, scale: float,
                     n_splits: int = 1) -> torch.Tensor:
     """:func:`attn_latent_paged` on the tensor cores, bfloat16 cache and result.
-    A tile is ``bm`` (16 or 64) consecutive (token, head) rows of one entry,
+    A tile is ``bm`` (16, 32 or 64) consecutive (token, head) rows of one entry,
     counted token by token with the heads innermost; ``tile_row0`` is a tile's
     first row within its entry.  With ``n_splits`` > 1 every tile's keys are cut
     into that many parts, which a second kernel merges."""
@@ -1089,7 +1089,7 @@ def attn_latent_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, pag
         _need(t.dtype == torch.int32, "attn_latent_mma: int32 metadata")
     _need(q.dtype == torch.float32 and out.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and q.shape == out.shape,
           "attn_latent_mma: q float32, out and cache bfloat16")
-    _need(bm in LATENT_MMA_TILES, "attn_latent_mma: tiles of 16 or 64 rows")
+    _need(bm in LATENT_MMA_TILES, "attn_latent_mma: tiles of 16, 32 or 64 rows")
     n_heads, rank = q.shape[1], q.shape[2]
     (q_row, q_head), (o_row, o_head) = _head_layout(q, n_heads, rank, "attn_latent_mma q"), _head_layout(out, n_heads, rank, "attn_latent_mma out")
     _need(o_row % 2 == 0 and o_head % 2 == 0, "attn_latent_mma: out vectors on 4-byte boundaries")

@@ -167,9 +167,8 @@ class LatentAttention(Part):
                                 max(int(layout.ctx_start[i]) + q_len[i] for i in portions),
                                 put([i for i in range(r) for _ in range(q_len[i])]))
         # tiles of (token, head) rows over the latents: every entry, or only the single tokens beside such portions
-        small, large = ops.LATENT_MMA_TILES
         rows = [(0 if prompt is not None and n > 1 else n * self.heads) for n in q_len]
-        bm = small if max(rows) <= small else large
+        bm = next((t for t in ops.LATENT_MMA_TILES if max(rows) <= t), ops.LATENT_MMA_TILES[-1])
         row_entry, row0 = [], []
         for i, n in enumerate(rows):
             for r0 in range(0, n, bm):
