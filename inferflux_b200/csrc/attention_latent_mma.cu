@@ -19,7 +19,6 @@
 #include "common.cuh"
 
 namespace {
-constexpr int BN = 64;            // latents per tile
 constexpr int PAD = 8;            // bfloat16 elements of padding per shared-memory row (keeps ldmatrix conflict-free)
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -59,20 +58,23 @@ struct LatentTiles {
   const int* entry_ctx_start;
 };
 
-// MT: row tiles of 16 per block (BM = 16 MT); RT: R padded to 64 RT columns.
-template <int MT, int RT>
+// MT: row tiles of 16 per block (BM = 16 MT); RT: R padded to 64 RT columns; NARROW: tiles of 32 latents instead of
+// 64, so that two blocks of 16 rows fit an SM at every rank (taken when there are more blocks than SMs).
+template <int MT, int RT, bool NARROW>
 __global__ void __launch_bounds__(256)
 attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restrict__ out, HeadLayout ol,
                        const bf16* __restrict__ cache, long long page_stride, int page_size, int page_shift,
                        LatentTiles b, int n_heads, int rank, float scale, int n_splits,
                        float* __restrict__ part_o, float* __restrict__ part_ml) {
+  constexpr bool BY_R = MT <= 2 && RT >= 2;
+  constexpr int BN = NARROW ? 32 : 64;
   constexpr int BM = 16 * MT, RP = 64 * RT, LD = RP + PAD, LDP = BN + PAD, LDS = BN + 4;
   // S is shared out over the 8 warps in one of two ways.  By keys (NP == 1): a warp takes one row tile and MT of the 8
   // key tiles over all of R.  By R (NP > 1, taken for the low tiles of decode steps where the sums over R would
   // otherwise be one long chain of dependent products): a warp takes one row tile, all 8 key tiles and 1/NP of R,
   // and the NP partial scores are added when the softmax reads them.
-  constexpr int NP = (MT <= 2 && RT >= 2) ? 8 / MT : 1;
-  constexpr int NT_S = NP > 1 ? 8 : MT;
+  constexpr int NP = BY_R ? 8 / MT : 1;
+  constexpr int NT_S = BY_R ? BN / 8 : MT;
   pdl_enter();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);                    // [BM][LD]
@@ -102,14 +104,30 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
     const int r = idx / (LD - rank), c = rank + idx % (LD - rank);
     qs[r * LD + c] = __float2bfloat16_rn(0.0f);                     // qs and cs are contiguous: r runs over both
   }
-  for (int idx = tid; idx < BM * rank; idx += blockDim.x) {
-    const int r = idx / rank, d = idx - r * rank;
-    float v = 0.0f;
-    if (r < n_rows) {
+  if (((ql.row | ql.head) & 3) == 0 && ((uintptr_t)q & 15) == 0) {
+    // sixteen threads a row, 16 bytes a load: one division per row instead of two per element
+    for (int r = tid >> 4; r < BM; r += 16) {
       const int rr = row0 + r, t = rr / n_heads, h = rr - t * n_heads;
-      v = q[(size_t)(tok0 + t) * ql.row + (size_t)h * ql.head + d];
+      const float4* src = reinterpret_cast<const float4*>(q + (size_t)(tok0 + t) * ql.row + (size_t)h * ql.head);
+      for (int c = tid & 15; c < (rank >> 2); c += 16) {
+        const float4 v = r < n_rows ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<unsigned*>(&lo);
+        u.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(qs + r * LD + 4 * c) = u;
+      }
     }
-    qs[r * LD + d] = __float2bfloat16_rn(v);
+  } else {
+    for (int idx = tid; idx < BM * rank; idx += blockDim.x) {
+      const int r = idx / rank, d = idx - r * rank;
+      float v = 0.0f;
+      if (r < n_rows) {
+        const int rr = row0 + r, t = rr / n_heads, h = rr - t * n_heads;
+        v = q[(size_t)(tok0 + t) * ql.row + (size_t)h * ql.head + d];
+      }
+      qs[r * LD + d] = __float2bfloat16_rn(v);
+    }
   }
   for (int r = tid; r < BM; r += blockDim.x) {
     row_m[r] = -INFINITY;
@@ -121,10 +139,17 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
   auto load_tile = [&](int kt, int buf) {
     bf16* dst = cs + (size_t)buf * BN * LD;
     const int chunks = rank >> 3;
-    for (int j = warp; j < BN; j += 8) {
+    // the pages of this warp's latents are looked up side by side (one wait for memory, not one per latent)
+    int my_page = -1;
+    if (lane < BN / 8) {
+      const int key = kt * BN + warp + 8 * lane;
+      if (key <= kend) my_page = bt[key >> page_shift];
+    }
+#pragma unroll
+    for (int jj = 0; jj < BN / 8; ++jj) {
+      const int j = warp + 8 * jj;
       const int key = kt * BN + j;
-      int page = -1;
-      if (key <= kend) page = bt[key >> page_shift];
+      const int page = __shfl_sync(0xffffffffu, my_page, jj);
       bf16* d = dst + j * LD;
       if (page >= 0) {
         const bf16* src = cache + (size_t)page * page_stride + (size_t)(key & (page_size - 1)) * rank;
@@ -189,17 +214,27 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
     // ---- softmax of the tile: a warp takes BM / 8 rows, a lane two keys of a row
     for (int r = warp * (BM / 8); r < (warp + 1) * (BM / 8); ++r) {
       const int p = row_pos[r];                                      // -1 hides every key from a row that does not exist
-      const int key = kt * BN + 2 * lane;
-      const bool v0 = key <= p, v1 = key + 1 <= p;
-      float2 sc = *reinterpret_cast<const float2*>(ss + r * LDS + 2 * lane);
+      constexpr int KPL = BN / 32;                                   // keys a lane
+      const int key = kt * BN + KPL * lane;
+      const bool v0 = key <= p, v1 = KPL > 1 && key + 1 <= p;
+      float sc0, sc1 = 0.0f;
+      if constexpr (KPL == 2) {
+        float2 sc = *reinterpret_cast<const float2*>(ss + r * LDS + 2 * lane);
 #pragma unroll
-      for (int part = 1; part < NP; ++part) {
-        const float2 more = *reinterpret_cast<const float2*>(ss + (part * BM + r) * LDS + 2 * lane);
-        sc.x += more.x;
-        sc.y += more.y;
+        for (int part = 1; part < NP; ++part) {
+          const float2 more = *reinterpret_cast<const float2*>(ss + (part * BM + r) * LDS + 2 * lane);
+          sc.x += more.x;
+          sc.y += more.y;
+        }
+        sc0 = sc.x;
+        sc1 = sc.y;
+      } else {
+        sc0 = ss[r * LDS + lane];
+#pragma unroll
+        for (int part = 1; part < NP; ++part) sc0 += ss[(part * BM + r) * LDS + lane];
       }
-      const float s0 = v0 ? sc.x * scale : -INFINITY;
-      const float s1 = v1 ? sc.y * scale : -INFINITY;
+      const float s0 = v0 ? sc0 * scale : -INFINITY;
+      const float s1 = v1 ? sc1 * scale : -INFINITY;
       const float m_old = row_m[r];
       const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
       float p0 = 0.0f, p1 = 0.0f, alpha = 1.0f;
@@ -208,10 +243,17 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
         p0 = v0 ? expf(s0 - m_new) : 0.0f;
         p1 = v1 ? expf(s1 - m_new) : 0.0f;
       }
-      const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
-      *reinterpret_cast<__nv_bfloat162*>(ps + r * LDP + 2 * lane) = pp;
       // the sum is taken over the weights as they enter the product
-      const float sum = warp_sum(__low2float(pp) + __high2float(pp));
+      float sum;
+      if constexpr (KPL == 2) {
+        const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
+        *reinterpret_cast<__nv_bfloat162*>(ps + r * LDP + 2 * lane) = pp;
+        sum = warp_sum(__low2float(pp) + __high2float(pp));
+      } else {
+        const bf16 pb = __float2bfloat16_rn(p0);
+        ps[r * LDP + lane] = pb;
+        sum = warp_sum(__bfloat162float(pb));
+      }
       if (lane == 0) { row_m[r] = m_new; row_l[r] = row_l[r] * alpha + sum; row_a[r] = alpha; }
     }
     __syncthreads();
@@ -326,18 +368,19 @@ __global__ void attn_latent_merge_kernel(const float* __restrict__ part_o, const
   }
 }
 
-template <int MT, int RT>
+template <int MT, int RT, bool NARROW>
 size_t smem_bytes() {
-  constexpr int BM = 16 * MT, LD = 64 * RT + PAD, NP = (MT <= 2 && RT >= 2) ? 8 / MT : 1;
+  constexpr bool BY_R = MT <= 2 && RT >= 2;
+  constexpr int BM = 16 * MT, LD = 64 * RT + PAD, NP = BY_R ? 8 / MT : 1, BN = NARROW ? 32 : 64;
   return (size_t)(BM + 2 * BN) * LD * 2 + (size_t)BM * (BN + PAD) * 2 + (size_t)NP * BM * (BN + 4) * 4 + (size_t)4 * BM * 4;
 }
 
-template <int MT, int RT>
+template <int MT, int RT, bool NARROW>
 int launch_mma(const float* q, HeadLayout ql, bf16* out, HeadLayout ol, const bf16* cache, long long page_stride,
                int page_size, LatentTiles b, int n_tiles, int n_heads, int rank, float scale, int n_splits,
                float* part_o, float* part_ml, cudaStream_t stream) {
-  const size_t smem = smem_bytes<MT, RT>();
-  auto kern = attn_latent_mma_kernel<MT, RT>;
+  const size_t smem = smem_bytes<MT, RT, NARROW>();
+  auto kern = attn_latent_mma_kernel<MT, RT, NARROW>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -359,20 +402,24 @@ int launch_mma(const float* q, HeadLayout ql, bf16* out, HeadLayout ol, const bf
 // The largest rank the kernel takes (multiples of 8 up to it).
 IFX_API int ifx_attn_latent_mma_max_rank() { return 512; }
 
-// Into how many splits the keys of every tile are cut: enough blocks to fill the GPU (as many as it holds at
-// this rank's shared memory), but no split shorter than two key tiles.
-IFX_API int ifx_attn_latent_mma_plan(int n_tiles, int bm, int rank, int max_keys) {
-  if (n_tiles <= 0) return 1;
+namespace {
+int sm_count_now() {
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int rt = (rank + 63) / 64;
-  const int np = (bm <= 32 && rt >= 2) ? 128 / bm : 1;
-  const size_t smem = (size_t)(bm + 2 * BN) * (64 * rt + PAD) * 2 + (size_t)bm * (BN + PAD) * 2 + (size_t)np * bm * (BN + 4) * 4 + 4 * bm * 4;
-  int per_sm = (int)((size_t)(227 * 1024) / (smem + 1024));
-  per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
-  const int key_tiles = (max_keys + BN - 1) / BN;
-  int splits = (sms * per_sm) / n_tiles;
-  if (splits > key_tiles / 2) splits = key_tiles / 2;
+  return sms;
+}
+// Tiles of 16 rows take tiles of 32 latents when there are more blocks than SMs (two blocks then share an SM).
+bool narrow_tiles(int blocks) { return blocks > sm_count_now(); }
+}  // namespace
+
+// Into how many splits the keys of every tile are cut: enough blocks to fill the GPU (as many as it holds at
+// one block an SM), but no split shorter than 256 keys.
+IFX_API int ifx_attn_latent_mma_plan(int n_tiles, int bm, int rank, int max_keys) {
+  if (n_tiles <= 0) return 1;
+  const int sms = sm_count_now();
+  const int key_tiles = (max_keys + 63) / 64;
+  int splits = sms / n_tiles;                     // one block an SM where the tiles alone do not fill the GPU
+  if (splits > key_tiles / 4) splits = key_tiles / 4;      // no split shorter than 256 keys: below that a block's set-up outweighs its tiles
   return splits < 1 ? 1 : (splits > 64 ? 64 : splits);
 }
 
@@ -393,8 +440,16 @@ IFX_API int ifx_attn_latent_mma(const float* q, long long q_row, long long q_hea
   LatentTiles b{block_tables, bt_stride, tile_entry, tile_row0, entry_q_start, entry_q_len, entry_ctx_start};
   HeadLayout ql{q_row, q_head}, ol{o_row, o_head};
   const int rt = (rank + 63) / 64;
-#define IFX_LM(MT, RT) return launch_mma<MT, RT>(q, ql, (bf16*)out, ol, (const bf16*)cache, page_stride, page_size, b, n_tiles, \
+#define IFX_LM(MT, RT) return launch_mma<MT, RT, false>(q, ql, (bf16*)out, ol, (const bf16*)cache, page_stride, page_size, b, n_tiles, \
                                                  n_heads, rank, scale, n_splits, part_o, part_ml, stream)
+  if (bm == 16 && rt >= 2 && narrow_tiles(n_tiles * n_splits)) {
+#define IFX_LN(RT) return launch_mma<1, RT, true>(q, ql, (bf16*)out, ol, (const bf16*)cache, page_stride, page_size, b, n_tiles, \
+                                                  n_heads, rank, scale, n_splits, part_o, part_ml, stream)
+    if (rt <= 2) IFX_LN(2);
+    if (rt <= 4) IFX_LN(4);
+    IFX_LN(8);
+#undef IFX_LN
+  }
   if (bm == 16) {
     if (rt <= 1) IFX_LM(1, 1);
     if (rt <= 2) IFX_LM(1, 2);
