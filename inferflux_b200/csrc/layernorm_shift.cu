@@ -10,6 +10,7 @@
 // on what else is in the batch.  The mean is taken first and the deviations are squared afterwards (two
 // passes over the row in shared memory), which keeps the variance exact for rows with a large mean.
 #include "common.cuh"
+#include <initializer_list>
 
 namespace {
 
@@ -103,6 +104,110 @@ __global__ void add_layernorm_shift1_kernel(float* __restrict__ residual, const 
   }
 }
 
+// The two kernels above for rows whose length is a multiple of 4 (up to 8,192) on 16-byte boundaries: 256 threads a
+// row, thread t holds the groups of four elements t, t + 256, ... in registers between the sums and the output, so
+// a row is read once and written once.  SHIFT: the single-token kernel (row = entry; mu, state and shifted are used).
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(bf16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<unsigned*>(&a);
+  u.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TD, typename TO, int J, bool SHIFT>
+__global__ void __launch_bounds__(256)
+add_layernorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials, long long partial_stride,
+                         const float* __restrict__ weight, float eps, TO* __restrict__ out, float* __restrict__ out32,
+                         const int* __restrict__ rows, int hidden, int write_residual, const float* __restrict__ mu,
+                         float* __restrict__ state, const int* __restrict__ entry_slot, TO* __restrict__ shifted) {
+  pdl_enter();
+  __shared__ float red[32];
+  const int groups = hidden >> 2;
+  const int src = rows ? rows[blockIdx.x] : blockIdx.x;
+  float* r = residual + (size_t)src * hidden;
+  float4 v[J];
+  float sum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int gi = threadIdx.x + j * 256;
+    if (gi < groups) {
+      float4 x = ld4(r + 4 * gi);
+      if (delta) {
+        const TD* d = delta + (size_t)src * hidden + 4 * gi;
+        for (int p = 0; p < n_partials; ++p) {
+          const float4 y = ld4(d + (size_t)p * partial_stride);
+          x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+        }
+      }
+      v[j] = x;
+      sum += (x.x + x.y) + (x.z + x.w);
+    }
+  }
+  const float mean = block_sum(sum, red) / (float)hidden;
+  float sq = 0.0f;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    if (threadIdx.x + j * 256 < groups) {
+      const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
+      sq = fmaf(d, d, fmaf(c, c, fmaf(b, b, fmaf(a, a, sq))));
+    }
+  }
+  const float rstd = inv_sqrt_exact(block_sum(sq, red) / (float)hidden + eps);
+  float* st = SHIFT ? state + (size_t)entry_slot[blockIdx.x] * hidden : nullptr;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int gi = threadIdx.x + j * 256;
+    if (gi < groups) {
+      const float4 w = ld4(weight + 4 * gi);
+      if (write_residual) st4(r + 4 * gi, v[j]);
+      const float4 y = make_float4((v[j].x - mean) * rstd * w.x, (v[j].y - mean) * rstd * w.y, (v[j].z - mean) * rstd * w.z,
+                                   (v[j].w - mean) * rstd * w.w);
+      const size_t at = (size_t)blockIdx.x * hidden + 4 * gi;
+      if (out) st4(out + at, y);
+      if (out32) st4(out32 + at, y);
+      if (SHIFT) {
+        const float4 b = ld4(st + 4 * gi), m = ld4(mu + 4 * gi);
+        st4(st + 4 * gi, y);
+        st4(shifted + at, make_float4(y.x + (b.x - y.x) * m.x, y.y + (b.y - y.y) * m.y, y.z + (b.z - y.z) * m.z,
+                                      y.w + (b.w - y.w) * m.w));
+      }
+    }
+  }
+}
+
+template <typename TD, typename TO, bool SHIFT>
+int launch_layernorm_vec(float* residual, const void* delta, int n_partials, long long partial_stride, const float* weight,
+                         float eps, void* out, float* out32, const int* rows, int n_rows, int hidden, int write_residual,
+                         const float* mu, float* state, const int* entry_slot, void* shifted, cudaStream_t stream) {
+  int rc = IFX_ERR_UNSUPPORTED;
+#define IFX_LNV(J) case J: rc = launch_pdl(add_layernorm_vec_kernel<TD, TO, J, SHIFT>, dim3(n_rows), dim3(256), 0, stream, residual, \
+    (const TD*)delta, n_partials, partial_stride, weight, eps, (TO*)out, out32, rows, hidden, write_residual, mu, state,       \
+    entry_slot, (TO*)shifted); break;
+  switch ((hidden / 4 + 255) / 256) {
+    IFX_LNV(1) IFX_LNV(2) IFX_LNV(3) IFX_LNV(4) IFX_LNV(5) IFX_LNV(6) IFX_LNV(7) IFX_LNV(8)
+    default: return IFX_ERR_UNSUPPORTED;
+  }
+#undef IFX_LNV
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
+// Whether the vector kernels take these operands (a property of the row length and the addresses, never of the batch).
+bool vec_ok(int hidden, long long partial_stride, std::initializer_list<const void*> ptrs) {
+  if (hidden % 4 || hidden > 4 * 8 * 256 || (partial_stride & 3)) return false;
+  for (const void* p : ptrs)
+    if ((uintptr_t)p & 15) return false;
+  return true;
+}
+
 // One block per row.  h32: the normed rows in float32.  The block of an entry's first row reads what the slot
 // holds and, element by element after that, puts the entry's last row there; no other block touches the slot.
 template <typename TO>
@@ -173,6 +278,9 @@ template <typename TD, typename TO>
 int launch_add_layernorm(float* residual, const void* delta, int n_partials, long long partial_stride, const float* weight,
                          float eps, void* out, float* out32, const int* rows, int n_rows, int hidden, int write_residual,
                          cudaStream_t stream) {
+  if (vec_ok(hidden, partial_stride, {residual, delta, weight, out, out32}))
+    return launch_layernorm_vec<TD, TO, false>(residual, delta, n_partials, partial_stride, weight, eps, out, out32, rows, n_rows,
+                                               hidden, write_residual, nullptr, nullptr, nullptr, nullptr, stream);
   const size_t smem = (size_t)hidden * sizeof(float);
   auto kern = add_layernorm_kernel<TD, TO>;
   int rc = big_smem(kern, smem);
@@ -186,6 +294,9 @@ template <typename TD, typename TO>
 int launch_add_layernorm_shift1(float* residual, const void* delta, int n_partials, long long partial_stride,
                                 const float* weight, float eps, const float* mu, float* state, const int* entry_slot,
                                 void* out, void* shifted, int n_rows, int hidden, cudaStream_t stream) {
+  if (vec_ok(hidden, partial_stride, {residual, delta, weight, out, shifted, mu, state}))
+    return launch_layernorm_vec<TD, TO, true>(residual, delta, n_partials, partial_stride, weight, eps, out, nullptr, nullptr, n_rows,
+                                              hidden, 1, mu, state, entry_slot, shifted, stream);
   const size_t smem = (size_t)hidden * sizeof(float);
   auto kern = add_layernorm_shift1_kernel<TD, TO>;
   int rc = big_smem(kern, smem);
