@@ -72,6 +72,8 @@ class ParallelBlock:
     family = "arrangement"
     roles = {"norm": "norm", "shift": "shift", "mixer": "mixer", "feed_forward": "feed_forward"}
     optional_roles = frozenset({"shift", "feed_forward"})
+    #: Switches for tests and measurements: the two output projections as one product; sum, norm, shift and
+    #: state update of a single-token step as one kernel.  Off, the block runs its parts one by one.
     JOINT_OUTPUT = True
     FUSED_SINGLE = True
 

@@ -24,3 +24,18 @@ def test_random_then_models(tmp_path):
     info = _run("models", "--model", str(tmp_path / "m"))
     assert info["config"]["hidden_size"] == 96 and info["tensors"] == 3 * 12 + 3
     assert [g["window"] for g in info["cache_groups"]] == [None, 40]
+
+
+def test_random_then_models_of_the_second_architecture(tmp_path):
+    """The same two commands for a Kunonex configuration: the folder it writes is read back by its own keys,
+    and the description lists a latent stream per cache group and the state every run keeps."""
+    from helpers import KX_A
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(KX_A))
+    out = _run("random", "--config", str(cfg), "--seed", "4", "--out", str(tmp_path / "k"))
+    assert out["architecture"] == "Kunonex"
+    info = _run("models", "--model", str(tmp_path / "k"))
+    assert info["architecture"] == "Kunonex" and info["config"]["width"] == 64 and info["config"]["loop"]["times"] == 2
+    assert len(info["cache_groups"]) == 2
+    from inferflux_b200.config import load_config
+    assert load_config(str(tmp_path / "k")) == load_config(dict(KX_A))
