@@ -200,7 +200,7 @@ class StepRunner:
             token_ids=d_tok, positions=d_pos, entry_q_start=d_qs, entry_q_len=d_ql, entry_ctx_start=d_cs,
             entry_slot=d_sl, block_tables=d_tabs, slot_maps=d_sm, want_rows=d_want, n_want=len(want_rows),
             max_q_len=int(lens.max()),
-            max_ctx_len=int((starts + lens).max()) if widths is None else max(out_widths) * ps,
+            max_ctx_len=int((starts + lens).max()) if widths is None or not out_widths else max(out_widths) * ps,
             page_size=ps, kv=self.kv_storage, dtype=self.dtype, device=self.device, extras=extras)
 
     def build_context(self, entries: Sequence[StepEntry]) -> StepContext:

@@ -339,6 +339,38 @@ def test_model_whole_one_by_one_and_in_portions(dtype, name):
 
 @gpu
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kind", ["mingru", "latent_attention"])
+def test_models_of_one_kind_of_mixer(dtype, kind):
+    """Only recurrent layers (no paged cache at all: the step runs on state slots alone) and only attention
+    layers (latents of three different ranks: three cache groups), each looped as a whole."""
+    base = KX["A"]
+    if kind == "mingru":
+        layers = [base["layers"][1], base["layers"][3], dict(base["layers"][1], mlp=None)]
+    else:
+        layers = [base["layers"][0], base["layers"][2], KX["C"]["layers"][2] | {"mixer": dict(KX["C"]["layers"][2]["mixer"])}]
+    cfg = dict(base, layers=layers, loop=dict(start=0, stop=3, times=2))
+    model, runner, w = _runner_for(cfg, dtype, 33, tokens=512)
+    assert len(model.kv_needs) == (0 if kind == "mingru" else 3)
+    toks = random_tokens(cfg["vocab"], 90, 34)
+    want = plain.forward(cfg, w, toks)
+    assert _rel(_logits_in_steps(runner, "w", toks, [90]), want) < PTOL[dtype]
+    assert _rel(_logits_in_steps(runner, "c", toks, [40, 1, 1, 1, 1, 2, 30, 1]), want) < PTOL[dtype]
+    runner.kv.check(), runner.slots.check()
+    if dtype == torch.float32:
+        # the scheduler and the sampler over the same kind of model: what Engine.generate continues a prompt with
+        # is what the step function's logits of prompt + continuation, run whole, have as their largest
+        from inferflux_b200 import Engine, SamplingParams, StepEntry
+        eng = Engine.from_config(dict(cfg), seed=2, dtype="float32", kv_cache_tokens=256, max_seqs=4, chunked_prefill_tokens=16)
+        prompts = [random_tokens(cfg["vocab"], n, 35 + n) for n in (3, 37)]
+        for p, g in zip(prompts, eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))):
+            seq = p + g.tokens
+            logits = eng.run_step([StepEntry("v", seq, list(range(len(p) - 1, len(seq) - 1)))])
+            eng.runner.end("v")
+            assert logits.argmax(-1).tolist() == g.tokens
+
+
+@gpu
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "E"])
 def test_batches_of_unequal_requests_and_reused_slots(dtype, name):
     """Four requests of unequal length, portions beside single tokens, against each alone; then four more
