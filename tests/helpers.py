@@ -146,7 +146,11 @@ KX_D = dict(KX_C, loop=dict(start=2, stop=3, times=1), logit_scale=2.0)
 KX_E = dict(architecture="Kunonex", width=128, vocab=200, norm=dict(eps=1e-6), logit_scale=0.7,
             layers=[_kx_attn(2, 128, 128, 48, 64, 0.09, ff=160), _kx_gru(128, ff=96), _kx_attn(3, 128, 128, 64, 40, 0.09)],
             loop=dict(start=0, stop=1, times=2))
-KX = {"A": KX_A, "B": KX_B, "C": KX_C, "D": KX_D, "E": KX_E}
+# sizes that are no multiple of 4 or 8 anywhere: the kernels' plain (not vectorised) paths and the library products
+KX_F = dict(architecture="Kunonex", width=50, vocab=77, norm=dict(eps=2e-6), logit_scale=0.9,
+            layers=[_kx_gru(30, ff=45), _kx_attn(2, 10, 6, 12, 14, 0.3, ff=35), _kx_attn(3, 6, 10, 9, 11, 0.4)],
+            loop=dict(start=1, stop=2, times=2))
+KX = {"A": KX_A, "B": KX_B, "C": KX_C, "D": KX_D, "E": KX_E, "F": KX_F}
 
 
 def kunonex_tensors(cfg: dict, seed: int, sharpen: float = 6.0, lively: float = 12.0):

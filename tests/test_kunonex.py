@@ -102,7 +102,7 @@ def _load(part, tensors, dtype):
 
 @gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden", [40, 100, 1536])
+@pytest.mark.parametrize("hidden", [40, 50, 100, 1536, 9000])       # rows in registers, and (50, 9000) the plain kernel
 def test_layernorm_alone(dtype, hidden):
     from inferflux_b200.parts import LayerNorm
     from inferflux_b200.parts.base import PartialSums
@@ -142,10 +142,10 @@ def test_embedding_alone(dtype):
 
 @gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows", [3, 40])
-def test_polynorm_feed_forward_alone(dtype, rows):
+@pytest.mark.parametrize("rows,inter", [(3, 136), (40, 136), (5, 135), (9, 2304)])   # three kernels by the row's length
+def test_polynorm_feed_forward_alone(dtype, rows, inter):
     from inferflux_b200.parts import PolyNormFF
-    h, inter = 96, 136
+    h = 96
     part = PolyNormFF(dict(name="mlp", hidden=h, intermediate=inter, eps=2e-6), "l", dtype, DEV)
     w = {"l.mlp.up": _rand((inter, h), 4, 0.2), "l.mlp.up.b": _rand((inter,), 5, 0.3), "l.mlp.down": _rand((h, inter), 6, 0.2),
          "l.mlp.down.b": _rand((h,), 7, 0.3), "l.mlp.act": torch.tensor([0.7, -0.4, 0.25, 0.1])}
@@ -315,7 +315,7 @@ def _logits_in_steps(runner, rid, toks, sizes):
 
 @gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_model_whole_one_by_one_and_in_portions(dtype, name):
     """Every layer's residual stream is not compared here; the logits at every position are, for three ways
     of cutting the same prompt.  In float32 the three agree with each other almost to the bit."""
