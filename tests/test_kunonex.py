@@ -1,5 +1,5 @@
 """The Kunonex architecture against its plain restatement (plain_kunonex.py):
-every mechanism alone through its part and kernels, then whole models of four
+every mechanism alone through its part and kernels, then whole models of six
 tiny configurations that differ in every size and option, stepped whole, token
 by token, in portions down to two tokens, in mixed batches over a pool so
 small that pages and state slots are used again, through bin/trace_run and
