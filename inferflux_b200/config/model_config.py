@@ -274,7 +274,12 @@ class KunonexConfig(ModelConfig):
                 raise ConfigError(f"{where}: 'mixer' must be an object")
             sizes = {}
             for key in cls.MIXERS[kind]:
-                sizes[key] = _require_number(mixer, key, where) if key == "scale" else _require_int(mixer, key)
+                if key != "scale":
+                    sizes[key] = _require_int(mixer, key)
+                elif mixer.get("scale") is None:
+                    sizes[key] = float(sizes["dim"]) ** -0.5           # the usual scale where a configuration gives none
+                else:
+                    sizes[key] = _require_number(mixer, key, where)
             mlp = entry.get("mlp")
             ff, ff_kind = 0, ""
             if mlp is not None:

@@ -47,6 +47,9 @@ def test_config_is_read_from_its_own_keys():
         (0, None), (4, 0), (1, 0), (2, 0), (4, 1), (1, 1), (2, 1), (3, None)]
     assert [(i, t) for i, t in plain.layer_runs(KX["A"])] == [(0, None), (1, 0), (2, 0), (1, 1), (2, 1), (3, None)]
     assert "feed_forward" not in spec.layers[2].parts and spec.layers[4].arrangement == "junction"
+    unscaled = copy.deepcopy(KX["A"])
+    del unscaled["layers"][0]["mixer"]["scale"]
+    assert load_config(unscaled).layers[0].mixer["scale"] == 24 ** -0.5      # absent: one over the root of dim
     no_loop = build_spec(load_config(copy.deepcopy(KX["C"])))
     assert [r.layer for r in no_loop.schedule] == [0, 1, 2] and len(no_loop.layers) == 3
     for breaker, text in [(lambda d: d["layers"][0].update(type="conv"), "type"), (lambda d: d.pop("width"), "width"),
