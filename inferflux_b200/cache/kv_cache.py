@@ -121,9 +121,15 @@ class KVCacheManager:
                 seq.version += 1
         seq.reserved = max(seq.reserved, seq.length + n_new)
 
+    def _kept_blocks(self, group: int) -> int:
+        """Blocks at the start of a sequence that a window never passes: those that hold one of the first
+        tokens the group keeps visible."""
+        keep = getattr(self.needs[group], "keep_first", 0) or 0
+        return (keep + self.page_size - 1) // self.page_size
+
     def advance(self, rid: Hashable, n_new: int) -> None:
         """The step wrote ``n_new`` tokens: move the length on and give back the
-        pages that a window has passed."""
+        pages that a window has passed (never those of kept first tokens)."""
         seq = self._seqs[rid]
         if seq.length + n_new > seq.reserved:
             raise RuntimeError(f"request {rid!r}: advance beyond the reserved pages")
@@ -131,9 +137,10 @@ class KVCacheManager:
         for g in range(self.num_groups):
             first = self._first_needed_block(g, seq.length)
             table = seq.tables[g]
-            gone = [table[b] for b in range(min(first, len(table))) if table[b] >= 0]
+            span = range(self._kept_blocks(g), min(first, len(table)))
+            gone = [table[b] for b in span if table[b] >= 0]
             if gone:
-                for b in range(min(first, len(table))):
+                for b in span:
                     table[b] = -1
                 self.pools[g].free(gone)
                 seq.version += 1

@@ -326,3 +326,165 @@ class KunonexConfig(ModelConfig):
         if self.loop_times:
             out["loop"] = {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times}
         return out
+
+
+def _sub(d: Dict[str, Any], key: str, where: str, optional: bool = False) -> Optional[Dict[str, Any]]:
+    v = d.get(key)
+    if v is None and optional:
+        return None
+    if not isinstance(v, dict):
+        raise ConfigError(f"{where}: '{key}' must be an object")
+    return v
+
+
+@dataclass(frozen=True)
+class PemoraxLayer:
+    """One layer of a Pemorax model as config.json gives it: the mixer's sizes and constants (checked, defaults
+    filled in) and its feed-forward (``None`` = none; ``kind`` ``dense`` with ``ff``, or ``moe`` with ``ff`` of
+    one expert, ``experts`` and ``top``)."""
+
+    type: str = ""
+    mixer: Dict[str, Any] = field(default_factory=dict)
+    mlp: Optional[Dict[str, Any]] = None
+
+
+@dataclass(frozen=True)
+class PemoraxConfig(ModelConfig):
+    """``Pemorax``: a decoder whose layers are listed one by one in config.json (``layers``: ``type``, the
+    mixer's sizes under ``mixer``, the feed-forward under ``mlp`` or null).  Every sublayer sits between two
+    RMS norms.  The mixer ``parallel`` is two mixers side by side on the same input: ``left`` grouped-query
+    attention (short convolution on q, k, v, interleaved rotary positions with an optional frequency scaling,
+    capped scores, a window that keeps the first tokens, a sink in the softmax, an output gate) and ``right``
+    retention (rotate-half positions, a fixed decay per head, a per-head unit norm, a silu gate); their normed
+    outputs are averaged.  Feed-forwards are dense (gelu) or routed experts (gated silu)."""
+
+    width: int = 0
+    vocab: int = 0
+    norm_eps: float = 1e-6
+    layers: List[PemoraxLayer] = field(default_factory=list)
+
+    ARCHITECTURE = "Pemorax"
+    MODEL_TYPE = "pemorax"
+
+    @staticmethod
+    def _rot(d: Dict[str, Any], where: str, dim: int) -> Dict[str, Any]:
+        rot = _sub(d, "rot", where, optional=True)
+        if rot is None:
+            return {"dims": 0, "base": 10000.0, "scaling": None}
+        dims = _require_int(rot, "dims", 0)
+        if dims % 2 or dims > dim:
+            raise ConfigError(f"{where}: rot.dims {dims} must be even and at most dim {dim}")
+        out = {"dims": dims, "base": _require_number(rot, "base", where + " rot"), "scaling": None}
+        if out["base"] <= 1.0:
+            raise ConfigError(f"{where}: rot.base must be above 1")
+        sc = _sub(rot, "scaling", where + " rot", optional=True)
+        if sc is not None:
+            out["scaling"] = {k: _require_number(sc, k, where + " rot.scaling") for k in ("factor", "original", "fast", "slow")}
+            if min(out["scaling"].values()) <= 0:
+                raise ConfigError(f"{where}: the numbers of rot.scaling must be positive")
+        return out
+
+    @classmethod
+    def _left(cls, m: Dict[str, Any], where: str) -> Dict[str, Any]:
+        heads, dim = _require_int(m, "heads"), _require_int(m, "dim")
+        out = {"heads": heads, "kv_heads": _require_int(m, "kv_heads") if m.get("kv_heads") is not None else heads,
+               "dim": dim, "vdim": _require_int(m, "vdim") if m.get("vdim") is not None else dim,
+               "conv": _require_int(m, "conv", 1) if m.get("conv") is not None else 0,
+               "scale": _require_number(m, "scale", where) if m.get("scale") is not None else float(dim) ** -0.5,
+               "softcap": _require_number(m, "softcap", where) if m.get("softcap") is not None else None,
+               "rot": cls._rot(m, where, dim), "mask": None}
+        if heads % out["kv_heads"]:
+            raise ConfigError(f"{where}: heads {heads} is not a multiple of kv_heads {out['kv_heads']}")
+        if out["conv"] > 8:
+            raise ConfigError(f"{where}: a convolution of {out['conv']} taps is not supported (at most 8)")
+        if out["softcap"] is not None and out["softcap"] <= 0:
+            raise ConfigError(f"{where}: softcap must be positive")
+        mask = _sub(m, "mask", where, optional=True)
+        if mask is not None:
+            out["mask"] = {"size": _require_int(mask, "size"),
+                           "keep_first": _require_int(mask, "keep_first", 0) if mask.get("keep_first") is not None else 0}
+        return out
+
+    @classmethod
+    def _right(cls, m: Dict[str, Any], where: str) -> Dict[str, Any]:
+        heads, dim = _require_int(m, "heads"), _require_int(m, "dim")
+        decay = m.get("decay")
+        if not isinstance(decay, list) or len(decay) != heads or any(
+                isinstance(x, bool) or not isinstance(x, (int, float)) or not 0.0 < float(x) <= 1.0 for x in decay):
+            raise ConfigError(f"{where}: 'decay' must list one number in (0, 1] for each of the {heads} heads")
+        return {"heads": heads, "dim": dim, "vdim": _require_int(m, "vdim") if m.get("vdim") is not None else dim,
+                "decay": [float(x) for x in decay], "rot": cls._rot(m, where, dim)}
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "PemoraxConfig":
+        width, vocab = _require_int(d, "width"), _require_int(d, "vocab")
+        eps = _require_number(_sub(d, "norm", "config.json"), "eps", "config.json norm")
+        if eps <= 0:
+            raise ConfigError(f"norm eps must be positive, got {eps}")
+        raw = d.get("layers")
+        if not isinstance(raw, list) or not raw:
+            raise ConfigError("config.json: 'layers' must be a non-empty list")
+        layers = []
+        for i, entry in enumerate(raw):
+            where = f"config.json layers[{i}]"
+            if not isinstance(entry, dict):
+                raise ConfigError(f"{where}: must be an object")
+            kind = entry.get("type")
+            if kind != "parallel":
+                raise ConfigError(f"{where}: type {kind!r} is not one of ['parallel']")
+            mixer = _sub(entry, "mixer", where)
+            sizes = {"left": cls._left(_sub(mixer, "left", where + " mixer"), where + " mixer.left"),
+                     "right": cls._right(_sub(mixer, "right", where + " mixer"), where + " mixer.right")}
+            mlp = _sub(entry, "mlp", where, optional=True)
+            ff = None
+            if mlp is not None:
+                ff_kind = mlp.get("kind")
+                if ff_kind == "dense":
+                    ff = {"kind": "dense", "ff": _require_int(mlp, "ff")}
+                elif ff_kind == "moe":
+                    router = _sub(mlp, "router", where + " mlp")
+                    ff = {"kind": "moe", "ff": _require_int(_sub(mlp, "expert", where + " mlp"), "ff"),
+                          "experts": _require_int(router, "experts"), "top": _require_int(router, "top")}
+                    if ff["top"] > ff["experts"]:
+                        raise ConfigError(f"{where}: router.top {ff['top']} exceeds router.experts {ff['experts']}")
+                else:
+                    raise ConfigError(f"{where}: mlp kind {ff_kind!r} is not one of ['dense', 'moe']")
+            layers.append(PemoraxLayer(type=kind, mixer=sizes, mlp=ff))
+        arch = d.get("architecture") or (d.get("architectures") or [cls.ARCHITECTURE])[0]
+        return cls(architectures=[str(arch)], model_type=str(d.get("model_type", "") or cls.MODEL_TYPE), width=width,
+                   vocab=vocab, norm_eps=eps, layers=layers)
+
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @property
+    def eos_token_id(self) -> Optional[int]:
+        return None
+
+    def to_dict(self) -> Dict[str, Any]:
+        """The config.json this configuration was read from (its own keys)."""
+        def rot(r):
+            if not r["dims"]:
+                return None
+            out = {"dims": r["dims"], "base": r["base"]}
+            if r["scaling"]:
+                out["scaling"] = dict(r["scaling"])
+            return out
+
+        def strip(m):
+            return {k: v for k, v in m.items() if v is not None}
+        layers = []
+        for l in self.layers:
+            left, right = dict(l.mixer["left"]), dict(l.mixer["right"])
+            left["rot"], right["rot"] = rot(left["rot"]), rot(right["rot"])
+            if not left["conv"]:
+                left["conv"] = None
+            mlp = None
+            if l.mlp and l.mlp["kind"] == "dense":
+                mlp = {"kind": "dense", "ff": l.mlp["ff"]}
+            elif l.mlp:
+                mlp = {"kind": "moe", "expert": {"ff": l.mlp["ff"]}, "router": {"experts": l.mlp["experts"], "top": l.mlp["top"]}}
+            layers.append({"type": l.type, "mixer": {"left": strip(left), "right": strip(right)}, "mlp": mlp})
+        return {"architecture": self.architecture, "width": self.width, "vocab": self.vocab,
+                "norm": {"eps": self.norm_eps}, "layers": layers}

@@ -11,6 +11,12 @@
 // of 32 keys, and serves prompt portions (any number of cached tokens before
 // them) and single decoded tokens alike.  A window w > 0 hides keys j <= p - w.
 //
+// Options (AttnOptions; all off for plain attention): values of another width than keys (`v_dim`); a cap on
+// the scores, s <- cap * tanh(s / cap); kept first tokens, which stay visible behind the window
+// (key j visible iff j <= p and (p - j < w or j < keep_first)); a sink, one more term of score 0 and no value
+// in the softmax's denominator, p_j = exp(s_j) / (1 + sum exp(s_j)); an output gate, every element of a
+// head's result times sigmoid of a float32 row given beside it.
+//
 // Tiles start at multiples of 32 keys and keys are added in index order, so in
 // float32 the result for a token does not depend on how the prompt was cut.
 #include "common.cuh"
@@ -29,15 +35,27 @@ struct AttnBatch {
   const int* entry_ctx_start; // [n_entries] tokens cached before them = position of the first new token
 };
 
+struct AttnOptions {
+  int v_dim;                  // width of a value head (keys are head_dim wide)
+  int v_head_stride;          // elements between the value heads of a page = page_size * v_dim
+  float softcap;              // 0 = none
+  int keep_first;             // first tokens that stay visible behind the window
+  int sink;                   // 1 = the denominator has one more term exp(0)
+  const float* gate;          // [N][gate_stride] float32 or null: out *= sigmoid(gate[row][head * v_dim + d])
+  int gate_parts; long long gate_part_stride; int gate_stride;
+};
+
 template <typename T, int NACC>
 __global__ void __launch_bounds__(256)
 attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long out_stride,
-                          PagedKV kv, AttnBatch b, int n_heads, int n_kv, int head_dim, float scale, int window) {
+                          PagedKV kv, AttnBatch b, int n_heads, int n_kv, int head_dim, float scale, int window,
+                          AttnOptions opt) {
   pdl_enter();
   extern __shared__ float smem[];
+  const int v_dim = opt.v_dim;
   float* qs = smem;                               // [BQ][head_dim]
   float* ks = qs + BQ * head_dim;                 // [BKEYS][head_dim + 1]
-  float* vs = ks + BKEYS * (head_dim + 1);        // [BKEYS][head_dim]
+  float* vs = ks + BKEYS * (head_dim + 1);        // [BKEYS][v_dim]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tile = blockIdx.x, head = blockIdx.y;
   const int e = b.tile_entry[tile];
@@ -49,7 +67,7 @@ attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __rest
   const int kvh = head / (n_heads / n_kv);
   const int* bt = b.block_tables + (size_t)e * b.bt_stride;
   const T* kc = (const T*)kv.k + (size_t)kvh * kv.head_stride;
-  const T* vc = (const T*)kv.v + (size_t)kvh * kv.head_stride;
+  const T* vc = (const T*)kv.v + (size_t)kvh * opt.v_head_stride;
 
   for (int idx = tid; idx < BQ * head_dim; idx += blockDim.x) {
     const int r = idx / head_dim, d = idx - r * head_dim;
@@ -57,7 +75,8 @@ attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __rest
   }
 
   const int r0 = warp * 2, r1 = r0 + 1;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+  // a sink is a key of score 0 without a value: the running maximum starts at 0 and the sum at exp(0)
+  float m[2] = {opt.sink ? 0.0f : -INFINITY, opt.sink ? 0.0f : -INFINITY}, l[2] = {opt.sink ? 1.0f : 0.0f, opt.sink ? 1.0f : 0.0f};
   float o[2][NACC];
 #pragma unroll
   for (int a = 0; a < NACC; ++a) { o[0][a] = 0.0f; o[1][a] = 0.0f; }
@@ -65,23 +84,33 @@ attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __rest
   const int kend = pos0 + rows - 1;               // last key any row of the tile may see
   int kstart = 0;
   if (window > 0) kstart = max(0, pos0 - window + 1) & ~(BKEYS - 1);
+  // with kept first tokens the tiles [0, keep_end) come first, then those from kstart on
+  const int keep_end = window > 0 ? min((opt.keep_first + BKEYS - 1) & ~(BKEYS - 1), kstart) : 0;
 
-  for (int k0 = kstart; k0 <= kend; k0 += BKEYS) {
+  for (int k0 = keep_end > 0 ? 0 : kstart; k0 <= kend; k0 += BKEYS) {
+    if (k0 >= keep_end && k0 < kstart) k0 = kstart;
     __syncthreads();
     for (int idx = tid; idx < BKEYS * head_dim; idx += blockDim.x) {
       const int j = idx / head_dim, d = idx - j * head_dim;
       const int key = k0 + j;
-      float kval = 0.0f, vval = 0.0f;
+      float kval = 0.0f;
       if (key <= kend) {
         const int page = bt[key >> kv.page_shift];
-        if (page >= 0) {
-          const size_t off = (size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * head_dim + d;
-          kval = Num<T>::to_f(kc[off]);
-          vval = Num<T>::to_f(vc[off]);
-        }
+        if (page >= 0)
+          kval = Num<T>::to_f(kc[(size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * head_dim + d]);
       }
       ks[j * (head_dim + 1) + d] = kval;
-      vs[j * head_dim + d] = vval;
+    }
+    for (int idx = tid; idx < BKEYS * v_dim; idx += blockDim.x) {
+      const int j = idx / v_dim, d = idx - j * v_dim;
+      const int key = k0 + j;
+      float vval = 0.0f;
+      if (key <= kend) {
+        const int page = bt[key >> kv.page_shift];
+        if (page >= 0)
+          vval = Num<T>::to_f(vc[(size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * v_dim + d]);
+      }
+      vs[j * v_dim + d] = vval;
     }
     __syncthreads();
     if (r0 < rows) {                               // warp-uniform
@@ -100,8 +129,10 @@ attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __rest
       for (int rr = 0; rr < 2; ++rr) {
         if (rr == 1 && !two) break;
         const int p = pos0 + r0 + rr;
-        const bool visible = key <= p && (window <= 0 || key > p - window);
-        const float s = visible ? (rr ? s1 : s0) * scale : -INFINITY;
+        const bool visible = key <= p && (window <= 0 || key > p - window || key < opt.keep_first);
+        float sc = (rr ? s1 : s0) * scale;
+        if (opt.softcap > 0.0f) sc = opt.softcap * tanhf(sc / opt.softcap);
+        const float s = visible ? sc : -INFINITY;
         const float m_new = fmaxf(m[rr], warp_max(s));
         if (m_new == -INFINITY) continue;          // nothing visible to this row yet (warp-uniform)
         const float alpha = expf(m[rr] - m_new);   // exp(-inf) = 0 on the first visible tile
@@ -116,7 +147,7 @@ attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __rest
 #pragma unroll
           for (int a = 0; a < NACC; ++a) {
             const int d = lane + 32 * a;
-            if (d < head_dim) o[rr][a] = fmaf(pjj, vs[j * head_dim + d], o[rr][a]);
+            if (d < v_dim) o[rr][a] = fmaf(pjj, vs[j * v_dim + d], o[rr][a]);
           }
         }
       }
@@ -127,19 +158,27 @@ attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __rest
     const int r = r0 + rr;
     if (r >= rows) continue;
     const float inv = l[rr] > 0.0f ? 1.0f / l[rr] : 0.0f;
-    T* orow = out + (size_t)(tok0 + r) * out_stride + (size_t)head * head_dim;
+    T* orow = out + (size_t)(tok0 + r) * out_stride + (size_t)head * v_dim;
 #pragma unroll
     for (int a = 0; a < NACC; ++a) {
       const int d = lane + 32 * a;
-      if (d < head_dim) orow[d] = Num<T>::from_f(o[rr][a] * inv);
+      if (d >= v_dim) continue;
+      float y = o[rr][a] * inv;
+      if (opt.gate) {
+        float g = 0.0f;
+        for (int s = 0; s < opt.gate_parts; ++s)
+          g += opt.gate[(size_t)s * opt.gate_part_stride + (size_t)(tok0 + r) * opt.gate_stride + (size_t)head * v_dim + d];
+        y *= 1.0f / (1.0f + expf(-g));
+      }
+      orow[d] = Num<T>::from_f(y);
     }
   }
 }
 
 template <typename T, int NACC>
 int launch_generic(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnBatch b,
-                   int n_tiles, int n_heads, int n_kv, int head_dim, float scale, int window, cudaStream_t stream) {
-  const size_t smem = ((size_t)BQ * head_dim + (size_t)BKEYS * (head_dim + 1) + (size_t)BKEYS * head_dim) * sizeof(float);
+                   int n_tiles, int n_heads, int n_kv, int head_dim, float scale, int window, AttnOptions opt, cudaStream_t stream) {
+  const size_t smem = ((size_t)BQ * head_dim + (size_t)BKEYS * (head_dim + 1) + (size_t)BKEYS * opt.v_dim) * sizeof(float);
   auto kern = attn_paged_generic_kernel<T, NACC>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -147,23 +186,50 @@ int launch_generic(const void* q, long long q_stride, void* out, long long out_s
   }
   dim3 grid(n_tiles, n_heads);
   const int ifx_rc = launch_pdl(kern, grid, dim3(256), smem, stream, (const T*)q, q_stride, (T*)out, out_stride, kv, b, n_heads, n_kv,
-                                head_dim, scale, window);
+                                head_dim, scale, window, opt);
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
 template <typename T>
 int dispatch_generic(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnBatch b,
-                     int n_tiles, int n_heads, int n_kv, int head_dim, float scale, int window, cudaStream_t stream) {
-  const int nacc = (head_dim + 31) / 32;
-  if (nacc <= 1) return launch_generic<T, 1>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, stream);
-  if (nacc <= 2) return launch_generic<T, 2>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, stream);
-  if (nacc <= 4) return launch_generic<T, 4>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, stream);
-  return launch_generic<T, 8>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, stream);
+                     int n_tiles, int n_heads, int n_kv, int head_dim, float scale, int window, AttnOptions opt, cudaStream_t stream) {
+  const int nacc = (opt.v_dim + 31) / 32;
+  if (nacc <= 1) return launch_generic<T, 1>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
+  if (nacc <= 2) return launch_generic<T, 2>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
+  if (nacc <= 4) return launch_generic<T, 4>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
+  return launch_generic<T, 8>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
 }
 }  // namespace
 
 // Query tiles are 16 tokens of one entry: tile_entry / tile_q0 list them.
-// head_dim: any positive size up to 256; n_heads must be a multiple of n_kv.
+// head_dim and v_dim: any positive size up to 256; n_heads must be a multiple of n_kv.  The options are
+// those of AttnOptions; gate: float32 slices [gate_parts][N][gate_stride] whose sum is the gate's argument.
+IFX_API int ifx_attn_paged_generic_ex(const void* q, long long q_stride, void* out, long long out_stride, int dtype,
+                                      void* k_layer, void* v_layer, long long page_stride, int page_size,
+                                      const int* block_tables, int bt_stride,
+                                      const int* tile_entry, const int* tile_q0, int n_tiles,
+                                      const int* entry_q_start, const int* entry_q_len, const int* entry_ctx_start,
+                                      int n_heads, int n_kv, int head_dim, float scale, int window,
+                                      int v_dim, float softcap, int keep_first, int sink,
+                                      const float* gate, int gate_parts, long long gate_part_stride, int gate_stride,
+                                      cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (head_dim < 1 || head_dim > 256 || v_dim < 1 || v_dim > 256 || n_kv < 1 || n_heads % n_kv) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
+  if (n_heads > 65535 || keep_first < 0 || softcap < 0.0f) return IFX_ERR_UNSUPPORTED;
+  PagedKV kv;
+  kv.k = k_layer; kv.v = v_layer; kv.page_stride = page_stride;
+  kv.head_stride = page_size * head_dim; kv.page_size = page_size; kv.page_shift = 0;
+  while ((1 << kv.page_shift) < page_size) ++kv.page_shift;
+  AttnBatch b{block_tables, bt_stride, tile_entry, tile_q0, entry_q_start, entry_q_len, entry_ctx_start};
+  AttnOptions opt{v_dim, page_size * v_dim, softcap, keep_first, sink, gate, gate_parts, gate_part_stride, gate_stride};
+  if (dtype == IFX_F32)
+    return dispatch_generic<float>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
+  if (dtype == IFX_BF16)
+    return dispatch_generic<bf16>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
+  return IFX_ERR_UNSUPPORTED;
+}
+
 IFX_API int ifx_attn_paged_generic(const void* q, long long q_stride, void* out, long long out_stride, int dtype,
                                    void* k_layer, void* v_layer, long long page_stride, int page_size,
                                    const int* block_tables, int bt_stride,
@@ -171,18 +237,8 @@ IFX_API int ifx_attn_paged_generic(const void* q, long long q_stride, void* out,
                                    const int* entry_q_start, const int* entry_q_len, const int* entry_ctx_start,
                                    int n_heads, int n_kv, int head_dim, float scale, int window,
                                    cudaStream_t stream) {
-  if (n_tiles <= 0) return 0;
-  if (head_dim < 1 || head_dim > 256 || n_kv < 1 || n_heads % n_kv) return IFX_ERR_UNSUPPORTED;
-  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
-  if (n_heads > 65535) return IFX_ERR_UNSUPPORTED;
-  PagedKV kv;
-  kv.k = k_layer; kv.v = v_layer; kv.page_stride = page_stride;
-  kv.head_stride = page_size * head_dim; kv.page_size = page_size; kv.page_shift = 0;
-  while ((1 << kv.page_shift) < page_size) ++kv.page_shift;
-  AttnBatch b{block_tables, bt_stride, tile_entry, tile_q0, entry_q_start, entry_q_len, entry_ctx_start};
-  if (dtype == IFX_F32)
-    return dispatch_generic<float>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, stream);
-  if (dtype == IFX_BF16)
-    return dispatch_generic<bf16>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, stream);
-  return IFX_ERR_UNSUPPORTED;
+  return ifx_attn_paged_generic_ex(q, q_stride, out, out_stride, dtype, k_layer, v_layer, page_stride, page_size,
+                                   block_tables, bt_stride, tile_entry, tile_q0, n_tiles, entry_q_start, entry_q_len,
+                                   entry_ctx_start, n_heads, n_kv, head_dim, scale, window, head_dim, 0.0f, 0, 0,
+                                   nullptr, 0, 0, 0, stream);
 }

@@ -1,0 +1,185 @@
+// A short causal convolution over time on every channel of a stacked projection, rotary positions on the
+// query and key heads, and the write of keys and values into the paged cache, in one kernel:
+//
+//   y_t[c] = sum_{j < taps} w[c][j] * u_{t - taps + 1 + j}[c]        u = the projection's float32 sums,
+//                                                                    zeros before the sequence's start
+//   rotation of the first `rot_dims` dimensions of each query and key head, pairs either interleaved
+//   (2i, 2i+1) or split in halves (i, i + rot_dims/2):  (a, b) -> (a cos - b sin,  b cos + a sin)
+//   with the step's cos/sin tables [token][rot_dims/2];  values are convolved only.
+//
+// The last taps-1 projected rows of every sequence live in the request's state slot ("tail"), so a prompt
+// may be cut anywhere: a token whose window reaches back before the step's first row reads the tail.  The
+// tail is brought up to date by a second kernel after all rows have been read.  Everything is float32 up to
+// the one rounding into the engine's type.  The rotation kernel alone serves mixers without a convolution
+// or a paged cache (it rotates q and k of a float32 projection in place).
+#include "common.cuh"
+
+namespace {
+constexpr int MAX_TAPS = 8;
+enum { LAYOUT_HALF = 0, LAYOUT_INTERLEAVED = 1 };
+
+struct ConvRope {
+  const float* proj; int parts; long long part_stride; int proj_stride;   // [parts][N][proj_stride]
+  const float* conv_w;        // [channels][taps] or null (no convolution)
+  int taps;
+  float* tail;                // [slots][taps-1][channels]
+  const int* row_entry;       // [N]
+  const int* entry_q_start;   // [entries]
+  const int* entry_q_len;
+  const int* entry_slot;
+  const float* cos_t; const float* sin_t; int rot_half; int layout;
+  int n_heads, n_kv, dim, vdim;
+  void* q_out;                // [N][n_heads * dim]
+  const int* slot_map;        // [N] page * page_size + offset, negative = do not store
+  void* k_cache; void* v_cache; long long page_stride; int page_size, page_shift;
+};
+
+__device__ __forceinline__ float proj_at(const ConvRope& p, int row, int c) {
+  float v = 0.0f;
+  for (int s = 0; s < p.parts; ++s) v += p.proj[(size_t)s * p.part_stride + (size_t)row * p.proj_stride + c];
+  return v;
+}
+
+// The convolved value of channel c for the token at row `row`, the i-th new token of its entry.
+__device__ __forceinline__ float conv_at(const ConvRope& p, int row, int i, int slot, int channels, int c) {
+  if (!p.conv_w) return proj_at(p, row, c);
+  float y = 0.0f;
+  const float* w = p.conv_w + (size_t)c * p.taps;
+  for (int j = 0; j < p.taps; ++j) {
+    const int m = i - (p.taps - 1) + j;            // which token of the entry, negative = before this step
+    const float u = m >= 0 ? proj_at(p, row - (i - m), c)
+                           : p.tail[((size_t)slot * (p.taps - 1) + (p.taps - 1 + m)) * channels + c];
+    y = fmaf(w[j], u, y);
+  }
+  return y;
+}
+
+// The partner of dimension d under the rotation, or -1 if d does not rotate; `first` = d is the pair's first.
+__device__ __forceinline__ int rot_partner(int d, int rot_half, int layout, int& pair, bool& first) {
+  if (d >= 2 * rot_half) return -1;
+  if (layout == LAYOUT_INTERLEAVED) { pair = d >> 1; first = !(d & 1); return d ^ 1; }
+  first = d < rot_half;
+  pair = first ? d : d - rot_half;
+  return first ? d + rot_half : d - rot_half;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_rope_kv_write_kernel(ConvRope p) {
+  pdl_enter();
+  const int t = blockIdx.x;
+  const int e = p.row_entry[t];
+  const int i = t - p.entry_q_start[e];
+  const int slot = p.entry_slot[e];
+  const int cq = p.n_heads * p.dim, ck = p.n_kv * p.dim, cv = p.n_kv * p.vdim;
+  const int channels = cq + ck + cv;
+  const float* ct = p.cos_t + (size_t)t * p.rot_half;
+  const float* st = p.sin_t + (size_t)t * p.rot_half;
+  const int where = p.slot_map ? p.slot_map[t] : -1;
+  const long long page = where >= 0 ? (where >> p.page_shift) : 0;
+  const int off = where & (p.page_size - 1);
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    float y = conv_at(p, t, i, slot, channels, c);
+    if (c < cq + ck) {                             // a query or key channel: rotate
+      const int head = c / p.dim, d = c - head * p.dim;
+      int pair = 0; bool first = false;
+      const int pd = rot_partner(d, p.rot_half, p.layout, pair, first);
+      if (pd >= 0) {
+        const float z = conv_at(p, t, i, slot, channels, head * p.dim + pd);
+        const float co = ct[pair], si = st[pair];
+        y = first ? y * co - z * si : y * co + z * si;
+      }
+      if (c < cq) {
+        ((T*)p.q_out)[(size_t)t * cq + c] = Num<T>::from_f(y);
+      } else if (where >= 0) {
+        const int kh = head - p.n_heads;
+        ((T*)p.k_cache)[(size_t)page * p.page_stride + ((size_t)kh * p.page_size + off) * p.dim + d] = Num<T>::from_f(y);
+      }
+    } else if (where >= 0) {
+      const int cc = c - cq - ck;
+      const int vh = cc / p.vdim, d = cc - vh * p.vdim;
+      ((T*)p.v_cache)[(size_t)page * p.page_stride + ((size_t)vh * p.page_size + off) * p.vdim + d] = Num<T>::from_f(y);
+    }
+  }
+}
+
+// After the rows have been read: the tail becomes the last taps-1 rows of (old tail ++ the entry's new rows).
+__global__ void __launch_bounds__(256)
+conv_tail_update_kernel(ConvRope p) {
+  pdl_enter();
+  const int e = blockIdx.x;
+  const int channels = p.n_heads * p.dim + p.n_kv * p.dim + p.n_kv * p.vdim;
+  const int keep = p.taps - 1;
+  const int len = p.entry_q_len[e], r0 = p.entry_q_start[e];
+  float* tail = p.tail + (size_t)p.entry_slot[e] * keep * channels;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
+    float v[MAX_TAPS];
+#pragma unroll
+    for (int s = 0; s < MAX_TAPS; ++s) {
+      if (s >= keep) break;
+      const int m = len + s;                       // index into (old tail ++ new rows)
+      v[s] = m < keep ? tail[(size_t)m * channels + c] : proj_at(p, r0 + m - keep, c);
+    }
+#pragma unroll
+    for (int s = 0; s < MAX_TAPS; ++s) {
+      if (s >= keep) break;
+      tail[(size_t)s * channels + c] = v[s];
+    }
+  }
+}
+
+// Rotation in place of `n_rot_heads` heads of width `dim` that start at column `col0` of float32 rows.
+__global__ void __launch_bounds__(256)
+rotate_heads_kernel(float* __restrict__ x, int row_stride, int col0, int n_rot_heads, int dim,
+                    const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_half, int layout) {
+  pdl_enter();
+  const int t = blockIdx.x;
+  float* row = x + (size_t)t * row_stride + col0;
+  const float* ct = cos_t + (size_t)t * rot_half;
+  const float* st = sin_t + (size_t)t * rot_half;
+  for (int w = threadIdx.x; w < n_rot_heads * rot_half; w += blockDim.x) {
+    const int h = w / rot_half, i = w - h * rot_half;
+    const int d0 = layout == LAYOUT_INTERLEAVED ? 2 * i : i;
+    const int d1 = layout == LAYOUT_INTERLEAVED ? 2 * i + 1 : i + rot_half;
+    const float a = row[h * dim + d0], b = row[h * dim + d1];
+    const float co = ct[i], si = st[i];
+    row[h * dim + d0] = a * co - b * si;
+    row[h * dim + d1] = b * co + a * si;
+  }
+}
+}  // namespace
+
+IFX_API int ifx_conv_rope_kv_write(const float* proj, int parts, long long part_stride, int proj_stride,
+                                   const float* conv_w, int taps, float* tail,
+                                   const int* row_entry, const int* entry_q_start, const int* entry_q_len,
+                                   const int* entry_slot, int n_tokens, int n_entries,
+                                   const float* cos_t, const float* sin_t, int rot_half, int layout,
+                                   int n_heads, int n_kv, int dim, int vdim,
+                                   void* q_out, int dtype, const int* slot_map, void* k_cache, void* v_cache,
+                                   long long page_stride, int page_size, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (taps > MAX_TAPS || (conv_w && taps < 1) || 2 * rot_half > dim) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
+  ConvRope p{proj, parts, part_stride, proj_stride, conv_w, conv_w ? taps : 1, tail, row_entry, entry_q_start, entry_q_len,
+             entry_slot, cos_t, sin_t, rot_half, layout, n_heads, n_kv, dim, vdim, q_out, slot_map, k_cache, v_cache,
+             page_stride, page_size, 0};
+  while ((1 << p.page_shift) < page_size) ++p.page_shift;
+  int rc = dtype == IFX_BF16 ? launch_pdl(conv_rope_kv_write_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, p)
+                             : launch_pdl(conv_rope_kv_write_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, p);
+  if (rc) return rc;
+  if (conv_w && taps > 1) {
+    const int channels = n_heads * dim + n_kv * dim + n_kv * vdim;
+    rc = launch_pdl(conv_tail_update_kernel, dim3(n_entries, (channels + 1023) / 1024), dim3(256), 0, stream, p);
+    if (rc) return rc;
+  }
+  return IFX_LAUNCH_CHECK();
+}
+
+IFX_API int ifx_rotate_heads(float* x, int row_stride, int col0, int n_rot_heads, int dim, const float* cos_t,
+                             const float* sin_t, int rot_half, int layout, int n_tokens, cudaStream_t stream) {
+  if (n_tokens <= 0 || rot_half <= 0 || n_rot_heads <= 0) return 0;
+  if (2 * rot_half > dim) return IFX_ERR_UNSUPPORTED;
+  const int rc = launch_pdl(rotate_heads_kernel, dim3(n_tokens), dim3(256), 0, stream, x, row_stride, col0, n_rot_heads,
+                            dim, cos_t, sin_t, rot_half, layout);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}

@@ -412,3 +412,36 @@ IFX_API int ifx_convert(const void* src, int src_dtype, void* dst, int dst_dtype
 }
 
 IFX_STAMP_READER(ifx_stamps_elementwise)
+
+// ---- gelu (tanh form) over float32 sums, rounded once into the engine's type -----------------------
+// out = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))),  z = the sum of the input's slices
+template <typename T>
+__global__ void gelu_tanh_kernel(const float* __restrict__ z, int parts, long long part_stride, T* __restrict__ out,
+                                 long long out_stride, int cols, long long total) {
+  pdl_enter();
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    float v = 0.0f;
+    for (int s = 0; s < parts; ++s) v += z[(size_t)s * part_stride + idx];
+    const float y = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    const long long m = idx / cols;
+    out[m * out_stride + (idx - m * cols)] = Num<T>::from_f(y);
+  }
+}
+
+IFX_API int ifx_gelu_tanh(const float* z, int parts, long long part_stride, void* out, int out_dtype, long long out_stride,
+                          int m, int cols, cudaStream_t stream) {
+  const long long total = (long long)m * cols;
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  int rc;
+  if (out_dtype == IFX_F32)
+    rc = launch_pdl(gelu_tanh_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, z, parts, part_stride, (float*)out, out_stride, cols, total);
+  else if (out_dtype == IFX_BF16)
+    rc = launch_pdl(gelu_tanh_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, z, parts, part_stride, (bf16*)out, out_stride, cols, total);
+  else
+    return IFX_ERR_UNSUPPORTED;
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}

@@ -1,0 +1,235 @@
+// Routed experts: every token runs `top` of `experts` small feed-forwards and adds their results, weighted.
+//
+//   z = the router's float32 logits of a token;  chosen = the `top` largest (lowest index first among equals);
+//   weight_k = exp(z_k) / sum over the chosen exp(z)                                           (route)
+//   the (token, choice) pairs are sorted by expert into tiles of TILE rows, each tile one expert's (group)
+//   act = silu(x Wg_e^T) * (x Wu_e^T)   per tile, rows gathered from the tokens                 (expert_product)
+//   y   = act Wd_e^T                    per tile, float32
+//   out[token] = sum_k weight_k y[pair]  in the order of the choices                            (combine)
+//
+// Nothing here visits the host: the number of tiles that a step can need at most (pairs / TILE + experts) is
+// launched, and tiles beyond those in use return at once.  A pair's result does not depend on where in a tile
+// it lands (every output element adds its K products in index order), so the sort's order does not show.
+// The products are FFMA with float32 sums for either element type.
+#include "common.cuh"
+
+namespace {
+constexpr int MAX_TOP = 16;
+
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float* __restrict__ logits, int n_tokens, int experts, int top,
+                 int* __restrict__ chosen, float* __restrict__ weights) {
+  pdl_enter();
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= n_tokens) return;
+  const float* z = logits + (size_t)t * experts;
+  int ids[MAX_TOP]; float vals[MAX_TOP];
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY; int arg = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      bool taken = false;
+      for (int u = 0; u < k; ++u) taken |= ids[u] == e;
+      const float v = z[e];
+      if (!taken && (v > best || (v == best && e < arg))) { best = v; arg = e; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    ids[k] = arg; vals[k] = best;
+  }
+  float sum = 0.0f;
+  for (int k = 0; k < top; ++k) sum += expf(vals[k] - vals[0]);      // vals[0] is the largest
+  if (lane < top) {
+    // (a loop, not an index: the arrays stay in registers)
+    for (int k = 0; k < top; ++k)
+      if (k == lane) {
+        chosen[(size_t)t * top + k] = ids[k];
+        weights[(size_t)t * top + k] = expf(vals[k] - vals[0]) / sum;
+      }
+  }
+}
+
+// One block: counts per expert, tiles per expert, a place for every pair.
+//   tile_expert[max_tiles]: the expert of each tile or -1;  sorted_pair[max_tiles * tile]: the pair at each sorted
+//   row or -1;  pair_row[pairs]: the sorted row of each pair.
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ chosen, int pairs, int experts, int tile, int max_tiles,
+                 int* __restrict__ tile_expert, int* __restrict__ sorted_pair, int* __restrict__ pair_row) {
+  pdl_enter();
+  extern __shared__ int sm[];
+  int* count = sm;                 // [experts]
+  int* first = count + experts;    // [experts] first sorted row of the expert
+  int* cursor = first + experts;   // [experts]
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) { count[e] = 0; cursor[e] = 0; }
+  for (int i = threadIdx.x; i < max_tiles * tile; i += blockDim.x) sorted_pair[i] = -1;
+  for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_expert[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&count[chosen[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0;
+    for (int e = 0; e < experts; ++e) {
+      first[e] = t * tile;
+      const int n = (count[e] + tile - 1) / tile;
+      for (int k = 0; k < n; ++k) tile_expert[t + k] = e;
+      t += n;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = chosen[i];
+    const int r = first[e] + atomicAdd(&cursor[e], 1);
+    sorted_pair[r] = i;
+    pair_row[i] = r;
+  }
+}
+
+// C tile = A rows (gathered) x W_e^T.  SWIGLU: W_e is [2 * n_out][K] (gate rows, then up rows) and the tile's
+// columns are n_out wide: out = silu(gate) * up in TO.  Otherwise W_e is [n_out][K] and out is float32.
+// BM = 16 * TM rows a tile.
+template <typename TA, typename TW, typename TO, int TM, bool SWIGLU>
+__global__ void __launch_bounds__(256)
+moe_product_kernel(const TA* __restrict__ A, long long lda, int gather_div /* 0: rows are sorted rows; else token = pair / gather_div */,
+                   const TW* __restrict__ W, const int* __restrict__ tile_expert, const int* __restrict__ sorted_pair,
+                   TO* __restrict__ C, long long ldc, int n_out, int K) {
+  constexpr int BM = 16 * TM, BN = 64, BK = 16;
+  constexpr int TN = SWIGLU ? 2 : 4;                // per thread: TM x TN outputs (SWIGLU: of gate and of up each)
+  pdl_enter();
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Ws[BK][BN + 4];
+  __shared__ int rows[BM];
+  const int tile = blockIdx.y;
+  const int e = tile_expert[tile];
+  if (e < 0) return;
+  const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+  const int cols = SWIGLU ? BN / 2 : BN;            // output columns per block
+  const int n0 = blockIdx.x * cols;
+  const TW* We = W + (size_t)e * (SWIGLU ? 2 : 1) * n_out * K;
+  if (tid < BM) {
+    const int pair = sorted_pair[tile * BM + tid];
+    rows[tid] = pair < 0 ? -1 : (gather_div ? pair / gather_div : tile * BM + tid);
+  }
+  __syncthreads();
+  float acc[TM][4];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int idx = tid; idx < BM * BK; idx += 256) {
+      const int r = idx / BK, k = idx - r * BK;
+      const int src = rows[r];
+      As[k][r] = (src >= 0 && k0 + k < K) ? Num<TA>::to_f(A[(size_t)src * lda + k0 + k]) : 0.0f;
+    }
+    for (int idx = tid; idx < BN * BK; idx += 256) {
+      const int c = idx / BK, k = idx - c * BK;
+      int wrow;                                      // which row of W_e feeds the tile's local column c
+      if (SWIGLU) wrow = c < cols ? n0 + c : n_out + n0 + (c - cols);
+      else wrow = n0 + c;
+      const bool ok = (SWIGLU ? (c < cols ? n0 + c : n0 + c - cols) : n0 + c) < n_out && k0 + k < K;
+      Ws[k][c] = ok ? Num<TW>::to_f(We[(size_t)wrow * K + k0 + k]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float a[TM], w[4];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+      if (SWIGLU) {
+        w[0] = Ws[kk][tx * 2]; w[1] = Ws[kk][tx * 2 + 1]; w[2] = Ws[kk][cols + tx * 2]; w[3] = Ws[kk][cols + tx * 2 + 1];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w[j] = Ws[kk][tx * 4 + j];
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int r = ty * TM + i;
+    if (rows[r] < 0) continue;
+    TO* crow = C + (size_t)(tile * BM + r) * ldc;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int n = n0 + tx * TN + j;
+      if (n >= n_out) continue;
+      if (SWIGLU) {
+        const float g = acc[i][j], u = acc[i][2 + j];
+        crow[n] = Num<TO>::from_f(g / (1.0f + expf(-g)) * u);
+      } else {
+        crow[n] = Num<TO>::from_f(acc[i][j]);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_row, const float* __restrict__ weights,
+                   float* __restrict__ out, int hidden, int top) {
+  pdl_enter();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float acc = 0.0f;
+    for (int k = 0; k < top; ++k)
+      acc = fmaf(weights[(size_t)t * top + k], y[(size_t)pair_row[(size_t)t * top + k] * hidden + i], acc);
+    out[(size_t)t * hidden + i] = acc;
+  }
+}
+
+template <typename T, int TM>
+int launch_products(const void* x, const void* w_gate_up, const void* w_down, const int* tile_expert, const int* sorted_pair,
+                    void* act, float* y, int max_tiles, int hidden, int ff, int top, cudaStream_t stream) {
+  int rc = launch_pdl(moe_product_kernel<T, T, T, TM, true>, dim3((ff + 31) / 32, max_tiles), dim3(256), 0, stream,
+                      (const T*)x, (long long)hidden, top, (const T*)w_gate_up, tile_expert, sorted_pair, (T*)act,
+                      (long long)ff, ff, hidden);
+  if (rc) return rc;
+  return launch_pdl(moe_product_kernel<T, T, float, TM, false>, dim3((hidden + 63) / 64, max_tiles), dim3(256), 0, stream,
+                    (const T*)act, (long long)ff, 0, (const T*)w_down, tile_expert, sorted_pair, y, (long long)hidden,
+                    hidden, ff);
+}
+}  // namespace
+
+IFX_API int ifx_moe_route(const float* logits, int n_tokens, int experts, int top, int* chosen, float* weights,
+                          cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (top < 1 || top > MAX_TOP || top > experts) return IFX_ERR_UNSUPPORTED;
+  const int rc = launch_pdl(moe_route_kernel, dim3((n_tokens + 7) / 8), dim3(256), 0, stream, logits, n_tokens, experts, top,
+                            chosen, weights);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
+// Rows per tile for a step of n_tokens * top pairs: few pairs (single-token steps) take short tiles.
+IFX_API int ifx_moe_tile_rows(int pairs) { return pairs <= 256 ? 16 : 64; }
+
+// x [N][hidden], w_gate_up [experts][2 ff][hidden], w_down [experts][hidden][ff] of one element type `dtype`;
+// act [max_tiles * tile][ff] of that type, y [max_tiles * tile][hidden] float32, out [N][hidden] float32.
+// max_tiles >= pairs / tile + experts, tile = ifx_moe_tile_rows(pairs).
+IFX_API int ifx_moe_experts(const void* x, int dtype, const void* w_gate_up, const void* w_down, const int* chosen,
+                            const float* weights, int n_tokens, int hidden, int ff, int experts, int top, int tile,
+                            int max_tiles, int* tile_expert, int* sorted_pair, int* pair_row, void* act, float* y,
+                            float* out, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  const int pairs = n_tokens * top;
+  if ((tile != 16 && tile != 64) || max_tiles < pairs / tile + experts || experts > 4096) return IFX_ERR_UNSUPPORTED;
+  int rc = launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)3 * experts * sizeof(int), stream, chosen, pairs, experts,
+                      tile, max_tiles, tile_expert, sorted_pair, pair_row);
+  if (rc) return rc;
+  if (dtype == IFX_F32)
+    rc = tile == 16 ? launch_products<float, 1>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream)
+                    : launch_products<float, 4>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream);
+  else if (dtype == IFX_BF16)
+    rc = tile == 16 ? launch_products<bf16, 1>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream)
+                    : launch_products<bf16, 4>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream);
+  else
+    return IFX_ERR_UNSUPPORTED;
+  if (rc) return rc;
+  rc = launch_pdl(moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)y, (const int*)pair_row, weights, out,
+                  hidden, top);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}

@@ -1,0 +1,104 @@
+// A chain of root-mean-square norms around the residual sum, one block a row, everything float32:
+//
+//   ya = sum of a's slices                       (a mixer's or feed-forward's float32 sums)
+//   if wa:  ya = N(ya) * wa                      N(v) = v / sqrt(mean(v^2) + eps) over the row
+//   if b:   yb likewise with wb;  y = (ya + yb) / 2     (two branches side by side)      else y = ya
+//   if w_post:  y = N(y) * w_post                (a norm behind the sublayer)
+//   r = residual + y;   residual = r             (unless `rows` picks rows: then the residual stays)
+//   if out:  out = N(r) * w_next                 (the norm ahead of the next sublayer, engine type)
+//
+// Blocks that sandwich every sublayer between two norms, and mixers whose result is the mean of two normed
+// branches, run all of their row-wise arithmetic here in one pass over the row.  The number of threads
+// depends on the row length alone and every sum is added in a fixed order, so a row's result does not
+// depend on what else is in the batch.
+#include "common.cuh"
+
+namespace {
+struct ChainArgs {
+  const float* a; int a_parts; long long a_stride; const float* wa;
+  const float* b; int b_parts; long long b_stride; const float* wb;
+  const float* w_post;
+  float* residual;
+  const float* w_next;
+  void* out;
+  const int* rows;
+  int hidden;
+  float eps;
+};
+
+template <typename TO>
+__global__ void __launch_bounds__(1024)
+norm_chain_kernel(ChainArgs p) {
+  extern __shared__ float row[];                  // [hidden]: y
+  __shared__ float scratch[32];
+  pdl_enter();
+  const int H = p.hidden;
+  const int out_row = blockIdx.x;
+  const int r = p.rows ? p.rows[out_row] : out_row;
+  const float inv_h = 1.0f / (float)H;
+  // branch a
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = 0.0f;
+    if (p.a) for (int s = 0; s < p.a_parts; ++s) v += p.a[(size_t)s * p.a_stride + (size_t)r * H + i];
+    row[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  if (p.wa) {
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) * inv_h + p.eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = row[i] * inv * p.wa[i];
+  }
+  if (p.b) {
+    float sb = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = 0.0f;
+      for (int s = 0; s < p.b_parts; ++s) v += p.b[(size_t)s * p.b_stride + (size_t)r * H + i];
+      sb = fmaf(v, v, sb);
+    }
+    const float inv = p.wb ? 1.0f / sqrtf(block_sum(sb, scratch) * inv_h + p.eps) : 1.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = 0.0f;
+      for (int s = 0; s < p.b_parts; ++s) v += p.b[(size_t)s * p.b_stride + (size_t)r * H + i];
+      v = p.wb ? v * inv * p.wb[i] : v;
+      row[i] = 0.5f * (row[i] + v);
+    }
+  }
+  if (p.w_post) {
+    float sy = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) sy = fmaf(row[i], row[i], sy);
+    const float inv = 1.0f / sqrtf(block_sum(sy, scratch) * inv_h + p.eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = row[i] * inv * p.w_post[i];
+  }
+  float sr = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = p.residual[(size_t)r * H + i] + row[i];
+    if (!p.rows) p.residual[(size_t)r * H + i] = v;
+    row[i] = v;
+    sr = fmaf(v, v, sr);
+  }
+  if (p.out) {
+    const float inv = 1.0f / sqrtf(block_sum(sr, scratch) * inv_h + p.eps);
+    TO* o = (TO*)p.out + (size_t)out_row * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = Num<TO>::from_f(row[i] * inv * p.w_next[i]);
+  }
+}
+}  // namespace
+
+IFX_API int ifx_norm_chain(const float* a, int a_parts, long long a_stride, const float* wa,
+                           const float* b, int b_parts, long long b_stride, const float* wb,
+                           const float* w_post, float* residual, const float* w_next, void* out, int out_dtype,
+                           const int* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (hidden < 1 || hidden > 49152 || (out && !w_next)) return IFX_ERR_UNSUPPORTED;
+  ChainArgs p{a, a_parts, a_stride, wa, b, b_parts, b_stride, wb, w_post, residual, w_next, out, rows, hidden, eps};
+  int threads = (hidden + 3) / 4;                 // by the row length alone
+  threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : (threads + 31) / 32 * 32);
+  const size_t smem = (size_t)hidden * sizeof(float);
+  auto kern = out_dtype == IFX_BF16 ? norm_chain_kernel<bf16> : norm_chain_kernel<float>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int rc = launch_pdl(kern, dim3(n_rows), dim3(threads), smem, stream, p);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}

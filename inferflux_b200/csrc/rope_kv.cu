@@ -18,7 +18,8 @@
 
 // cos/sin tables [n_tokens, half] from positions and inverse frequencies.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
-                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int n_tokens, int half) {
+                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int n_tokens, int half,
+                                  double magnitude) {
   pdl_enter();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_tokens * half) return;
@@ -26,15 +27,15 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const doubl
   const double a = (double)positions[t] * inv_freq[i];
   double s, c;
   sincos(a, &s, &c);
-  cos_t[idx] = (float)c;
-  sin_t[idx] = (float)s;
+  cos_t[idx] = (float)(c * magnitude);     // a scaled encoding stretches both by one factor (1 = plain)
+  sin_t[idx] = (float)(s * magnitude);
 }
 
 IFX_API int ifx_rope_table(const int* positions, const double* inv_freq, float* cos_t, float* sin_t,
-                           int n_tokens, int half, cudaStream_t stream) {
+                           int n_tokens, int half, double magnitude, cudaStream_t stream) {
   const int total = n_tokens * half;
   if (total <= 0) return 0;
-  int ifx_rc = launch_pdl(rope_table_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, positions, inv_freq, cos_t, sin_t, n_tokens, half);
+  int ifx_rc = launch_pdl(rope_table_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, positions, inv_freq, cos_t, sin_t, n_tokens, half, magnitude);
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 

@@ -64,6 +64,8 @@ class Model:
         every = [self.embedding, self.final_norm, self.lm_head, *self.positions.values()]
         for parts in self._layer_parts:
             every += list(parts.values())
+        for p in list(every):                  # parts made of parts: theirs describe the step too
+            every += list(p.subparts()) if hasattr(p, "subparts") else []
         for p in every:
             key = getattr(p, "describe_key", None)
             if key is not None and key not in out:

@@ -42,7 +42,7 @@ def _lib():
                                         c_int, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.ifx_swiglu.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.ifx_convert.argtypes = [c_void_p, c_int, c_void_p, c_int, c_ll, c_void_p]
-        lib.ifx_rope_table.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.ifx_rope_table.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_double, c_void_p]
         lib.ifx_qkv_rope_kv_write.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                               c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                               c_int, c_void_p]
@@ -135,6 +135,34 @@ def _lib():
                                        c_void_p, c_int, c_void_p]
         lib.ifx_gather_latents.argtypes = [c_void_p, c_int, c_ll, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                            c_int, c_void_p]
+        c_dbl = ctypes.c_double
+        lib.ifx_norm_chain.argtypes = [c_void_p, c_int, c_ll, c_void_p, c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
+        lib.ifx_conv_rope_kv_write.argtypes = [c_void_p, c_int, c_ll, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                               c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                                               c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                               c_ll, c_int, c_void_p]
+        lib.ifx_rotate_heads.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_attn_paged_generic_ex.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int,
+                                                  c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                  c_void_p, c_int, c_int, c_int, c_float, c_int,
+                                                  c_int, c_float, c_int, c_int, c_void_p, c_int, c_ll, c_int, c_void_p]
+        lib.ifx_retention_segment.argtypes = []
+        lib.ifx_retention_scan.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float,
+                                           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+        lib.ifx_retention_finish.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_ll, c_int, c_int, c_int, c_float,
+                                             c_void_p]
+        lib.ifx_gelu_tanh.argtypes = [c_void_p, c_int, c_ll, c_void_p, c_int, c_ll, c_int, c_int, c_void_p]
+        lib.ifx_moe_route.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
+        lib.ifx_moe_tile_rows.argtypes = [c_int]
+        lib.ifx_moe_experts.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_void_p]
+        for name in ("ifx_norm_chain", "ifx_conv_rope_kv_write", "ifx_rotate_heads", "ifx_attn_paged_generic_ex",
+                     "ifx_retention_segment", "ifx_retention_scan", "ifx_retention_finish", "ifx_gelu_tanh",
+                     "ifx_moe_route", "ifx_moe_tile_rows", "ifx_moe_experts"):
+            getattr(lib, name).restype = c_int
         for name in ("ifx_add_layernorm", "ifx_add_layernorm_shift1", "ifx_token_shift", "ifx_embed_sinusoid_layernorm",
                      "ifx_polynorm", "ifx_mingru_segment", "ifx_mingru_scan", "ifx_latent_prep", "ifx_attn_latent_paged", "ifx_gate_heads",
                      "ifx_add_into", "ifx_add_rows_vector", "ifx_attn_latent_mma", "ifx_attn_latent_mma_plan",
@@ -244,13 +272,14 @@ def convert(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------- rotary
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
-    """cos/sin [N, half] float32 of positions[t] * inv_freq[i] (inv_freq float64 [half])."""
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+               magnitude: float = 1.0) -> None:
+    """cos/sin [N, half] float32 of positions[t] * inv_freq[i] (inv_freq float64 [half]), both times ``magnitude``."""
     n, half = positions.numel(), inv_freq.numel()
     _need(positions.dtype == torch.int32 and inv_freq.dtype == torch.float64, "rope_table: int32 positions, float64 inv_freq")
     _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
           and tuple(cos.shape) == (n, half) and tuple(sin.shape) == (n, half), "rope_table: cos/sin float32 [N, half]")
-    _check(_lib().ifx_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), n, half, _stream()),
+    _check(_lib().ifx_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), n, half, float(magnitude), _stream()),
            "rope_table")
 
 
@@ -1101,4 +1130,220 @@ def attn_latent_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, pag
                                       _ptr(block_tables), block_tables.stride(0), _ptr(tile_entry), _ptr(tile_row0), n_tiles,
                                       bm, _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_ctx_start), n_heads, rank,
                                       float(scale), n_splits, _ptr(part_o), _ptr(part_ml), _stream()), "attn_latent_mma")
+    return out
+
+
+# ------------------------------------------------- norm chains, convolution + rotation, retention, routed experts
+def _slices(t: Optional[torch.Tensor], n: int, width: int, what: str):
+    """(pointer, number of slices, elements between slices) of float32 sums given as [N, W] or [P, N, W]."""
+    if t is None:
+        return None, 0, 0
+    _need(t.dtype == torch.float32 and t.is_contiguous(), f"{what}: float32 contiguous sums")
+    if t.dim() == 3:
+        _need(tuple(t.shape[1:]) == (n, width), f"{what}: slices [P, {n}, {width}], got {tuple(t.shape)}")
+        return _ptr(t), t.shape[0], n * width
+    _need(tuple(t.shape) == (n, width), f"{what}: [{n}, {width}], got {tuple(t.shape)}")
+    return _ptr(t), 1, 0
+
+
+def norm_chain(residual: torch.Tensor, a: Optional[torch.Tensor], eps: float, w_a: Optional[torch.Tensor] = None,
+               b: Optional[torch.Tensor] = None, w_b: Optional[torch.Tensor] = None,
+               w_post: Optional[torch.Tensor] = None, w_next: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """One pass over every row, float32: ``y = a`` (``N(a) * w_a`` with a weight), with ``b`` the mean of the two
+    (normed) branches; ``y = N(y) * w_post`` with a weight; ``residual += y``; ``out = N(residual) * w_next``.
+    ``N(v) = v / sqrt(mean(v^2) + eps)``.  ``a`` and ``b`` are float32 ``[N, H]`` or slices ``[P, N, H]`` that are
+    added first.  With ``rows`` (int32) only those rows are computed, into ``out [R, H]``, and the residual is
+    left as it is."""
+    n, hidden = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "norm_chain: residual float32 contiguous")
+    for w in (w_a, w_b, w_post, w_next):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == hidden and w.is_contiguous()), "norm_chain: weights float32 [H]")
+    n_rows = rows.numel() if rows is not None else n
+    if rows is not None:
+        _need(rows.dtype == torch.int32, "norm_chain: rows int32")
+    ap, a_parts, a_stride = _slices(a, n, hidden, "norm_chain a")
+    bp, b_parts, b_stride = _slices(b, n, hidden, "norm_chain b")
+    if out is not None:
+        _need(out.is_contiguous() and tuple(out.shape) == (n_rows, hidden) and w_next is not None, "norm_chain: out [rows, H] and w_next")
+    _check(_lib().ifx_norm_chain(ap, a_parts, a_stride, _ptr(w_a), bp, b_parts, b_stride, _ptr(w_b), _ptr(w_post),
+                                 _ptr(residual), _ptr(w_next), _ptr(out), _code(out) if out is not None else F32,
+                                 _ptr(rows), n_rows, hidden, float(eps), _stream()), "norm_chain")
+    return out
+
+
+ROT_HALF, ROT_INTERLEAVED = 0, 1
+
+
+def conv_rope_kv_write(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int, tail: Optional[torch.Tensor],
+                       row_entry: torch.Tensor, entry_q_start: torch.Tensor, entry_q_len: torch.Tensor,
+                       entry_slot: torch.Tensor, n_entries: int, cos: torch.Tensor, sin: torch.Tensor, layout: int,
+                       n_heads: int, n_kv: int, dim: int, vdim: int, q_out: torch.Tensor, slot_map: torch.Tensor,
+                       k_layer: torch.Tensor, v_layer: torch.Tensor, page_stride: int, page_size: int) -> None:
+    """The first ``(n_heads + n_kv) * dim + n_kv * vdim`` columns of the float32 projection ``proj [N, W]`` (or
+    slices ``[P, N, W]``) are q, k and v heads side by side.  Every channel is convolved over time with its
+    ``taps`` weights ``conv_w [channels, taps]`` (None = no convolution), reading the rows before the step's
+    first from ``tail [slots, taps - 1, channels]``, which is then brought up to date; q and k heads are rotated
+    by ``cos``/``sin`` ``[N, r/2]`` in pairs ``(i, i + r/2)`` (``ROT_HALF``) or ``(2i, 2i + 1)``
+    (``ROT_INTERLEAVED``); q goes to ``q_out [N, n_heads * dim]``, k and v into the paged cache at ``slot_map``."""
+    n = q_out.shape[0]
+    channels = (n_heads + n_kv) * dim + n_kv * vdim
+    width = proj.shape[-1]
+    _need(proj.dtype == torch.float32 and proj.is_contiguous() and width >= channels, "conv_rope: float32 projection")
+    parts, pstride = (proj.shape[0], n * width) if proj.dim() == 3 else (1, 0)
+    if conv_w is not None:
+        _need(conv_w.dtype == torch.float32 and conv_w.is_contiguous() and tuple(conv_w.shape) == (channels, taps),
+              "conv_rope: conv weights float32 [channels, taps]")
+        if taps > 1:
+            _need(tail is not None and tail.dtype == torch.float32 and tail.is_contiguous()
+                  and tuple(tail.shape[1:]) == (taps - 1, channels), "conv_rope: tail float32 [slots, taps - 1, channels]")
+    _need(cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape == sin.shape
+          and cos.shape[0] == n, "conv_rope: cos/sin float32 [N, r/2]")
+    _need(q_out.is_contiguous() and tuple(q_out.shape) == (n, n_heads * dim) and k_layer.dtype == q_out.dtype,
+          "conv_rope: q_out [N, heads * dim] of the cache's type")
+    _check(_lib().ifx_conv_rope_kv_write(_ptr(proj), parts, pstride, width, _ptr(conv_w), int(taps), _ptr(tail),
+                                         _ptr(row_entry), _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_slot), n,
+                                         n_entries, _ptr(cos), _ptr(sin), cos.shape[1], layout, n_heads, n_kv, dim, vdim,
+                                         _ptr(q_out), _code(q_out), _ptr(slot_map), _ptr(k_layer), _ptr(v_layer),
+                                         page_stride, page_size, _stream()), "conv_rope_kv_write")
+    if conv_w is not None and taps > 1:
+        global launch_count
+        launch_count += 1
+
+
+def rotate_heads(x: torch.Tensor, col0: int, n_rot_heads: int, dim: int, cos: torch.Tensor, sin: torch.Tensor,
+                 layout: int) -> torch.Tensor:
+    """Rotates, in place, ``n_rot_heads`` heads of width ``dim`` that start at column ``col0`` of the float32 rows
+    ``x [N, W]``: the first ``2 * cos.shape[1]`` dimensions of each, paired by ``layout``."""
+    _need(x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1, "rotate_heads: float32 rows")
+    _need(cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape == sin.shape
+          and cos.shape[0] == x.shape[0], "rotate_heads: cos/sin float32 [N, r/2]")
+    _need(col0 + n_rot_heads * dim <= x.shape[1], "rotate_heads: heads beyond the row")
+    _check(_lib().ifx_rotate_heads(_ptr(x), x.stride(0), col0, n_rot_heads, dim, _ptr(cos), _ptr(sin), cos.shape[1], layout,
+                                   x.shape[0], _stream()), "rotate_heads")
+    return x
+
+
+def attn_paged_options(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer: torch.Tensor, v_layer: torch.Tensor,
+                       page_stride: int, page_size: int, block_tables: torch.Tensor, tile_entry: torch.Tensor,
+                       tile_q0: torch.Tensor, n_tiles: int, entry_q_start: torch.Tensor, entry_q_len: torch.Tensor,
+                       entry_ctx_start: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float, window: int,
+                       v_dim: int, softcap: float = 0.0, keep_first: int = 0, sink: bool = False,
+                       gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`attn_paged_generic` with values ``v_dim`` wide, a cap on the scores (``softcap * tanh(s / softcap)``,
+    0 = none), ``keep_first`` first tokens that stay visible behind the window, a sink (one more term ``exp(0)`` in
+    the denominator) and an output gate: ``gate`` = float32 ``[N, W]`` or ``[P, N, W]`` sums whose first
+    ``n_heads * v_dim`` columns go through a sigmoid and multiply the result element by element."""
+    _need(block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.stride(1) == 1,
+          "attn: block_tables int32 [R, B]")
+    _need(out.is_contiguous() and out.dtype == q.dtype and k_layer.dtype == q.dtype and out.shape[1] == n_heads * v_dim, "attn: types")
+    gp, g_parts, g_pstride, g_stride = None, 0, 0, 0
+    if gate is not None:
+        _need(gate.dtype == torch.float32 and gate.stride(-1) == 1 and gate.shape[-1] >= n_heads * v_dim, "attn: gate float32 rows")
+        gp = _ptr(gate)
+        if gate.dim() == 3:
+            g_parts, g_pstride, g_stride = gate.shape[0], gate.stride(0), gate.stride(1)
+        else:
+            g_parts, g_pstride, g_stride = 1, 0, gate.stride(0)
+    _check(_lib().ifx_attn_paged_generic_ex(_ptr(q), q_stride, _ptr(out), out.stride(0), _code(q), _ptr(k_layer),
+                                            _ptr(v_layer), page_stride, page_size, _ptr(block_tables),
+                                            block_tables.stride(0), _ptr(tile_entry), _ptr(tile_q0), n_tiles,
+                                            _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_ctx_start),
+                                            n_heads, n_kv, head_dim, float(scale), int(window), int(v_dim), float(softcap),
+                                            int(keep_first), 1 if sink else 0, gp, g_parts, g_pstride, g_stride, _stream()),
+           "attn_paged_options")
+    return out
+
+
+def retention_segment() -> int:
+    """Tokens per segment of the retention scan."""
+    return int(_lib().ifx_retention_segment())
+
+
+def retention_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, heads: int, dim: int, vdim: int,
+                   decay: torch.Tensor, k_scale: float, state: torch.Tensor, seg_entry: torch.Tensor, seg_t0: torch.Tensor,
+                   n_segments: int, entry_first_seg: torch.Tensor, entry_q_start: torch.Tensor, entry_q_len: torch.Tensor,
+                   entry_slot: torch.Tensor, n_entries: int, multi: bool, out: torch.Tensor) -> torch.Tensor:
+    """``S_t = decay_h S_{t-1} + (k_scale k_t) v_t^T``, ``o_t = S_t^T q_t`` per head over the step's entries, all
+    float32.  ``proj`` float32 ``[N, W]`` holds q, k (already rotated) and v heads from the given columns on;
+    ``state`` float32 ``[slots, heads, dim, vdim]``; ``out`` float32 ``[N, heads * vdim]``."""
+    n = proj.shape[0]
+    _need(proj.dtype == torch.float32 and proj.dim() == 2 and proj.stride(1) == 1, "retention: float32 projection rows")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+          "retention: state float32 [slots, heads, dim, vdim]")
+    _need(decay.dtype == torch.float32 and decay.numel() == heads, "retention: decay float32 [heads]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (n, heads * vdim), "retention: out float32")
+    seg_b = seg_start = None
+    if multi:
+        seg_b = torch.empty((n_segments, heads, dim, vdim), dtype=torch.float32, device=proj.device)
+        seg_start = torch.empty_like(seg_b)
+    _check(_lib().ifx_retention_scan(_ptr(proj), proj.stride(0), q_col, k_col, v_col, heads, dim, vdim, _ptr(decay),
+                                     float(k_scale), _ptr(state), _ptr(seg_entry), _ptr(seg_t0), n_segments,
+                                     _ptr(entry_first_seg), _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_slot),
+                                     n_entries, 1 if multi else 0, _ptr(seg_b), _ptr(seg_start), _ptr(out), _stream()),
+           "retention_scan")
+    if multi:
+        global launch_count
+        launch_count += 2
+    return out
+
+
+def retention_finish(o: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, heads: int, vdim: int, eps: float) -> torch.Tensor:
+    """``out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * silu(gate[t, h])``: ``o`` float32 ``[N, heads * vdim]``,
+    ``gate`` float32 rows (a view with any row stride), ``out`` rows of either type with any row stride."""
+    n = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and gate.dtype == torch.float32 and gate.stride(1) == 1
+          and out.stride(1) == 1 and tuple(out.shape) == (n, heads * vdim), "retention_finish: operands")
+    _check(_lib().ifx_retention_finish(_ptr(o), _ptr(gate), gate.stride(0), _ptr(out), _code(out), out.stride(0), n, heads,
+                                       vdim, float(eps), _stream()), "retention_finish")
+    return out
+
+
+def gelu_tanh(z: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))`` of float32 sums ``z [M, C]`` or ``[P, M, C]``."""
+    m, cols = out.shape
+    zp, parts, pstride = _slices(z, m, cols, "gelu_tanh")
+    _need(out.stride(1) == 1, "gelu_tanh: out rows")
+    _check(_lib().ifx_gelu_tanh(zp, parts, pstride, _ptr(out), _code(out), out.stride(0), m, cols, _stream()), "gelu_tanh")
+    return out
+
+
+def moe_route(logits: torch.Tensor, top: int):
+    """The ``top`` largest of every row of float32 ``logits [N, E]`` (lowest index first among equals) and the
+    softmax over them alone: (int32 ``[N, top]``, float32 ``[N, top]``)."""
+    n, experts = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "moe_route: float32 logits")
+    _need(1 <= top <= min(16, experts), f"moe_route: top {top} must be within 1..min(16, experts)")
+    chosen = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    _check(_lib().ifx_moe_route(_ptr(logits), n, experts, top, _ptr(chosen), _ptr(weights), _stream()), "moe_route")
+    return chosen, weights
+
+
+def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor,
+                weights: torch.Tensor) -> torch.Tensor:
+    """``out[t] = sum_k weights[t, k] * W_down[e] (silu(W_gate[e] x_t) * (W_up[e] x_t))``, ``e = chosen[t, k]``:
+    ``x [N, H]``, ``w_gate_up [E, 2F, H]`` (gate rows, then up rows), ``w_down [E, H, F]`` of one type; float32
+    ``[N, H]`` out.  The pairs are sorted by expert on the device and run as tiles of one expert each."""
+    n, hidden = x.shape
+    experts, two_f, _ = w_gate_up.shape
+    ff, top = two_f // 2, chosen.shape[1]
+    _need(x.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and x.dtype == w_gate_up.dtype == w_down.dtype,
+          "moe_experts: contiguous operands of one type")
+    _need(tuple(w_down.shape) == (experts, hidden, ff) and w_gate_up.shape[2] == hidden, "moe_experts: weight shapes")
+    pairs = n * top
+    tile = int(_lib().ifx_moe_tile_rows(pairs))
+    max_tiles = pairs // tile + experts
+    dev = x.device
+    tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    sorted_pair = torch.empty(max_tiles * tile, dtype=torch.int32, device=dev)
+    pair_row = torch.empty(pairs, dtype=torch.int32, device=dev)
+    act = torch.empty((max_tiles * tile, ff), dtype=x.dtype, device=dev)
+    y = torch.empty((max_tiles * tile, hidden), dtype=torch.float32, device=dev)
+    out = torch.empty((n, hidden), dtype=torch.float32, device=dev)
+    _check(_lib().ifx_moe_experts(_ptr(x), _code(x), _ptr(w_gate_up), _ptr(w_down), _ptr(chosen), _ptr(weights), n, hidden, ff,
+                                  experts, top, tile, max_tiles, _ptr(tile_expert), _ptr(sorted_pair), _ptr(pair_row),
+                                  _ptr(act), _ptr(y), _ptr(out), _stream()), "moe_experts")
+    global launch_count
+    launch_count += 3
     return out

@@ -1,3 +1,4 @@
 """Architectures.  Importing this package registers them."""
 from . import qwen2  # noqa: F401
 from . import kunonex  # noqa: F401
+from . import pemorax  # noqa: F401

@@ -13,6 +13,9 @@ from .shift import TokenShift
 from .recurrent import MinGRU
 from .latent_attention import LatentAttention
 from .junction import LoopEntry
+from .window_attention import WindowAttention
+from .retention import Retention
+from .side_by_side import SideBySide
 
 __all__ = ["Part", "KVNeed", "StateNeed", "RunInfo", "Linear", "RMSNorm", "RotaryHalf",
            "GQAttention", "SwiGLU", "PreNormBlock", "TokenEmbedding", "LinearHead", "LayerNorm", "PolyNormFF",

@@ -36,11 +36,14 @@ class KVNeed:
 
     streams: Tuple[CacheStream, ...]
     window: Optional[int] = None
+    keep_first: int = 0         # with a window: this many first tokens stay visible (and cached) for good
 
     @classmethod
-    def keys_and_values(cls, n_kv_heads: int, head_dim: int, window: Optional[int] = None) -> "KVNeed":
-        """``n_kv_heads * head_dim`` keys and as many values per token."""
-        return cls((CacheStream("k", n_kv_heads, head_dim), CacheStream("v", n_kv_heads, head_dim)), window)
+    def keys_and_values(cls, n_kv_heads: int, head_dim: int, window: Optional[int] = None,
+                        value_dim: Optional[int] = None, keep_first: int = 0) -> "KVNeed":
+        """``n_kv_heads * head_dim`` keys and as many values per token (values ``value_dim`` wide if given)."""
+        return cls((CacheStream("k", n_kv_heads, head_dim), CacheStream("v", n_kv_heads, value_dim or head_dim)),
+                   window, keep_first if window else 0)
 
     @property
     def elements_per_token(self) -> int:
@@ -64,6 +67,25 @@ class PartialSums:
     def __init__(self, tensor: torch.Tensor):
         self.tensor = tensor
         self.count = tensor.shape[0]
+
+
+class BranchMean:
+    """A mixer's result given as the mean of branches, each the float32 sums of one branch (a tensor or
+    :class:`PartialSums`) normed with a weight of its own: ``(N(a) * w_a + N(b) * w_b) / 2`` with
+    ``N(v) = v / sqrt(mean(v^2) + eps)``.  The norm that takes it computes it while it adds."""
+
+    def __init__(self, branches, eps: float):
+        self.branches = list(branches)          # [(sums, weight float32 [H]), ...]: two of them
+        self.eps = eps
+
+
+class NormedDelta:
+    """A sublayer's result that is to be normed before it joins the stream: ``N(value) * weight`` with ``value``
+    a tensor, :class:`PartialSums` or :class:`BranchMean`.  Blocks with a norm behind every sublayer hand this
+    to the next norm, which does both norms and the sum in one pass over the row."""
+
+    def __init__(self, value, weight: torch.Tensor, eps: float):
+        self.value, self.weight, self.eps = value, weight, eps
 
 
 class Part:
@@ -99,7 +121,9 @@ class Part:
     * ``junction``: ``forward(residual, ctx, run) -> None``: rewrites the
       float32 stream in place between layers (a loop's entry, say).
 
-    Any part may describe the step for its kernels (:meth:`describe_step`).
+    Any part may describe the step for its kernels (:meth:`describe_step`).  A part that is made of other
+    parts (two mixers side by side, say) lists them in :meth:`subparts`; the model asks those for their
+    descriptions too.
     """
 
     family = ""
@@ -109,6 +133,9 @@ class Part:
         self.prefix = prefix
         self.dtype = dtype
         self.device = device
+
+    def subparts(self) -> list:
+        return []
 
     # -- naming ---------------------------------------------------------
     @staticmethod

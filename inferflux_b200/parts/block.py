@@ -21,7 +21,7 @@ import torch
 
 from ..config.registry import register_part
 from ..kernels import ops
-from .base import PartialSums, RunInfo
+from .base import NormedDelta, PartialSums, RunInfo
 from .linear import Linear
 
 
@@ -157,5 +157,40 @@ class JunctionBlock:
         return None
 
 
+class SandwichBlock:
+    """A norm ahead of and a norm behind every sublayer:
+
+        residual += norm_1b(mixer(norm_1(residual)))
+        residual += norm_2b(feed_forward(norm_2(residual)))         (a layer may have no feed-forward)
+
+    A sublayer's result is not added here: it goes on as a :class:`NormedDelta` with the weight of the norm
+    behind it, and the next norm ahead (this block's second, the next block's first, or the model's last) norms
+    it, adds it to the stream and norms the stream in one kernel.  Norms of the kind ``rmsnorm`` take such a
+    delta."""
+
+    family = "arrangement"
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm",
+             "feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_post_norm": "norm"}
+    optional_roles = frozenset({"feed_forward_norm", "feed_forward", "feed_forward_post_norm"})
+
+    def __init__(self, parts: Dict[str, object], position_name: Optional[str]):
+        self.mixer_norm, self.mixer, self.mixer_post = parts["mixer_norm"], parts["mixer"], parts["mixer_post_norm"]
+        self.ff_norm, self.ff, self.ff_post = (parts.get(r) for r in ("feed_forward_norm", "feed_forward",
+                                                                      "feed_forward_post_norm"))
+        if (self.ff is None) != (self.ff_norm is None) or (self.ff is None) != (self.ff_post is None):
+            raise ValueError("a sandwich block has a feed-forward with both of its norms or none of the three")
+        self.position_name = position_name
+
+    def forward(self, residual: torch.Tensor, delta, ctx, run: RunInfo):
+        x = self.mixer_norm.forward(residual, delta)
+        position = ctx.position_tables.get(self.position_name) if self.position_name else None
+        a = NormedDelta(self.mixer.forward(x, ctx, run, position), self.mixer_post.weight, self.mixer_post.eps)
+        if self.ff is None:
+            return a
+        x2 = self.ff_norm.forward(residual, a)
+        return NormedDelta(self.ff.forward(x2, ctx), self.ff_post.weight, self.ff_post.eps)
+
+
+register_part("arrangement", "sandwich", SandwichBlock)
 register_part("arrangement", "parallel", ParallelBlock)
 register_part("arrangement", "junction", JunctionBlock)

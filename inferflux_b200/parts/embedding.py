@@ -22,7 +22,7 @@ from .linear import Linear
 
 
 class TokenEmbedding(Part):
-    """params: ``vocab``, ``hidden``, ``name`` (weight ``<name>.weight``)."""
+    """params: ``vocab``, ``hidden``, ``name`` (weight ``<name>.weight``) or ``weight_name`` (the table's full name)."""
 
     family = "embedding"
 
@@ -32,11 +32,16 @@ class TokenEmbedding(Part):
         self.table: torch.Tensor = None
 
     @classmethod
+    def _table_name(cls, prefix, params) -> str:
+        return params.get("weight_name") or cls.full_name(prefix, params, "weight")
+
+    @classmethod
     def weight_specs(cls, params, prefix) -> List[WeightSpec]:
-        return [WeightSpec(cls.full_name(prefix, params, "weight"), (int(params["vocab"]), int(params["hidden"])), MATRIX)]
+        return [WeightSpec(cls._table_name(prefix, params), (int(params["vocab"]), int(params["hidden"])), MATRIX,
+                           std=float(params.get("std", 0.02)))]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.table = tensors[self.full_name(self.prefix, self.params, "weight")].contiguous()
+        self.table = tensors[self._table_name(self.prefix, self.params)].contiguous()
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)

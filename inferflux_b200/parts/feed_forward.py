@@ -19,7 +19,7 @@ import torch
 from ..config.registry import register_part
 from ..kernels import ops
 from ..weights.loader import MATRIX, VECTOR, WeightSpec
-from .base import Part
+from .base import Part, PartialSums
 from .linear import Linear
 
 
@@ -117,5 +117,88 @@ class PolyNormFF(Part):
         return self.down.forward(self.inner(x, ctx), out_dtype=torch.float32)
 
 
+class GeluMLP(Part):
+    """``down( gelu(up(x)) )`` with the tanh form of gelu, ``0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))``,
+    and no biases.  The up projection leaves float32 sums; the activation rounds once into the engine's type.
+    params: ``hidden``, ``intermediate``, ``name`` (tensors ``<prefix>.<name>.{up,down}``)."""
+
+    family = "feed_forward"
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
+        self.up: Linear = None
+        self.down: Linear = None
+
+    @classmethod
+    def weight_specs(cls, params: Dict[str, Any], prefix: str) -> List[WeightSpec]:
+        h, i = int(params["hidden"]), int(params["intermediate"])
+        n = lambda leaf: cls.full_name(prefix, params, leaf)
+        return [WeightSpec(n("up"), (i, h), MATRIX), WeightSpec(n("down"), (h, i), MATRIX)]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
+        self.up, self.down = Linear(tensors.pop(n("up"))), Linear(tensors.pop(n("down")))
+
+    def forward(self, x: torch.Tensor, ctx):
+        z = self.up.forward(x, out_dtype=torch.float32, allow_partials=True, f32_sums=True)
+        act = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
+        ops.gelu_tanh(z.tensor if isinstance(z, PartialSums) else z, act)
+        return self.down.forward(act, out_dtype=torch.float32, allow_partials=True, f32_sums=True)
+
+
+class RoutedExperts(Part):
+    """A mixture of experts: every token runs the ``top`` experts with the largest router logits and adds their
+    results, weighted by the softmax over the chosen logits alone.
+
+        z = W_router x + b            float32 (x may be the engine type's rounding)
+        expert e: W_down_e ( silu(W_gate_e x) * (W_up_e x) ),  no biases
+
+    The experts' matrices are stacked at load; the (token, expert) pairs are sorted by expert on the device and
+    run as tiles of one expert each, so nothing waits for the host and a step of single tokens is captured like
+    any other.  params: ``hidden``, ``intermediate`` (of one expert), ``experts``, ``top``, ``name`` (tensors
+    ``<prefix>.<name>.router``, ``.router.b``, ``.e<i>.{gate,up,down}``)."""
+
+    family = "feed_forward"
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
+        self.experts, self.top = int(params["experts"]), int(params["top"])
+        if not 1 <= self.top <= min(self.experts, 16):
+            raise ValueError(f"routed_experts: top {self.top} must be within 1..min(experts, 16)")
+        self.router: Linear = None
+        self.gate_up: torch.Tensor = None
+        self.down: torch.Tensor = None
+
+    @classmethod
+    def weight_specs(cls, params: Dict[str, Any], prefix: str) -> List[WeightSpec]:
+        h, i, e = int(params["hidden"]), int(params["intermediate"]), int(params["experts"])
+        n = lambda leaf: cls.full_name(prefix, params, leaf)
+        specs = [WeightSpec(n("router"), (e, h), MATRIX, std=0.5), WeightSpec(n("router.b"), (e,), VECTOR, std=0.5)]
+        for k in range(e):
+            specs += [WeightSpec(n(f"e{k}.gate"), (i, h), MATRIX), WeightSpec(n(f"e{k}.up"), (i, h), MATRIX),
+                      WeightSpec(n(f"e{k}.down"), (h, i), MATRIX)]
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
+        self.router = Linear(tensors.pop(n("router")).float(), tensors.pop(n("router.b")))     # 32-bit whatever the engine
+        mats = [[tensors.pop(n(f"e{k}.{x}")) for x in ("gate", "up", "down")] for k in range(self.experts)]
+        kinds = {m.dtype for row in mats for m in row}
+        cast = (lambda m: m.float()) if len(kinds) > 1 else (lambda m: m)
+        self.gate_up = torch.stack([torch.cat([cast(g), cast(u)], dim=0) for g, u, _ in mats]).contiguous()
+        self.down = torch.stack([cast(d) for _, _, d in mats]).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        logits = self.router.forward(x, out_dtype=torch.float32)
+        chosen, weights = ops.moe_route(logits, self.top)
+        if x.dtype != self.gate_up.dtype:
+            x = ops.convert(x.contiguous(), torch.empty(x.shape, dtype=self.gate_up.dtype, device=x.device))
+        return ops.moe_experts(x.contiguous(), self.gate_up, self.down, chosen, weights)
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "gelu_mlp", GeluMLP)
+register_part("feed_forward", "routed_experts", RoutedExperts)
 register_part("feed_forward", "polynorm", PolyNormFF)

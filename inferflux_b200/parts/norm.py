@@ -15,11 +15,15 @@ import torch
 from ..config.registry import register_part
 from ..kernels import ops
 from ..weights.loader import VECTOR, WeightSpec
-from .base import Part, PartialSums
+from .base import BranchMean, NormedDelta, Part, PartialSums
 
 
 class RMSNorm(Part):
-    """params: ``hidden``, ``eps``, ``name`` (weight is ``<prefix>.<name>.weight``)."""
+    """params: ``hidden``, ``eps``, and the weight's name: ``name`` (weight is ``<prefix>.<name>.weight``) or
+    ``weight_name`` (the leaf itself, ``<prefix>.<weight_name>``).
+
+    ``delta`` may also be a :class:`NormedDelta` (a sublayer's result that is normed before it joins the
+    stream, itself possibly the mean of two normed branches): both norms and the sum are one kernel."""
 
     family = "norm"
 
@@ -30,12 +34,17 @@ class RMSNorm(Part):
         self.weight: Optional[torch.Tensor] = None
 
     @classmethod
+    def _weight_name(cls, prefix, params) -> str:
+        if params.get("weight_name"):
+            return ".".join(p for p in (prefix, params["weight_name"]) if p)
+        return cls.full_name(prefix, params, "weight")
+
+    @classmethod
     def weight_specs(cls, params: Dict[str, Any], prefix: str) -> List[WeightSpec]:
-        return [WeightSpec(cls.full_name(prefix, params, "weight"), (int(params["hidden"]),), VECTOR,
-                           init="one_plus_normal")]
+        return [WeightSpec(cls._weight_name(prefix, params), (int(params["hidden"]),), VECTOR, init="one_plus_normal")]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors[self.full_name(self.prefix, self.params, "weight")].to(torch.float32).contiguous()
+        self.weight = tensors[self._weight_name(self.prefix, self.params)].to(torch.float32).contiguous()
 
     def forward(self, residual: torch.Tensor, delta, out: Optional[torch.Tensor] = None,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -43,12 +52,37 @@ class RMSNorm(Part):
         float32 ``residual`` (unless ``rows`` picks rows, which leaves it
         untouched) and returns the normed rows in the engine's type."""
         n_partials = 1
-        if isinstance(delta, PartialSums):
-            delta, n_partials = delta.tensor, delta.count
         n_rows = rows.numel() if rows is not None else residual.shape[0]
         if out is None:
             out = torch.empty((n_rows, self.hidden), dtype=self.dtype, device=residual.device)
+        if isinstance(delta, NormedDelta):
+            return normed_sum(residual, delta, self.weight, out, rows)
+        if isinstance(delta, PartialSums):
+            delta, n_partials = delta.tensor, delta.count
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows, n_partials)
+
+
+def _sums(v) -> torch.Tensor:
+    """float32 sums as the chain kernel takes them: ``[N, H]`` or slices ``[P, N, H]``."""
+    if isinstance(v, PartialSums):
+        return v.tensor
+    if v.dtype != torch.float32:
+        raise TypeError("a normed delta is made of float32 sums; a part gave " + str(v.dtype))
+    return v
+
+
+def normed_sum(residual: torch.Tensor, delta: NormedDelta, w_next: Optional[torch.Tensor], out: Optional[torch.Tensor],
+               rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``residual += N(value) * delta.weight`` and, with ``w_next``, ``out = N(residual) * w_next``, in one kernel;
+    ``value`` may be the mean of two normed branches."""
+    v = delta.value
+    if isinstance(v, BranchMean):
+        if len(v.branches) != 2:
+            raise ValueError("the mean of normed branches is built for two branches")
+        (a, wa), (b, wb) = v.branches
+        return ops.norm_chain(residual, _sums(a), delta.eps, w_a=wa, b=_sums(b), w_b=wb, w_post=delta.weight,
+                              w_next=w_next, out=out, rows=rows)
+    return ops.norm_chain(residual, _sums(v), delta.eps, w_post=delta.weight, w_next=w_next, out=out, rows=rows)
 
 
 class LayerNorm(Part):

@@ -1,0 +1,175 @@
+"""``window_attention``: grouped-query attention with the options of newer
+decoder designs, each a parameter:
+
+  q, k, v (and a gate g) = one stacked projection of the normed input, float32 sums
+  ``conv`` taps          a short causal convolution over time on every channel of q, k and v, straight after
+                         the projection: y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros before the sequence
+  rotation               of the first ``rot_dims`` dimensions of every query and key head by the layer's
+                         position table, pairs ``interleaved`` (2i, 2i+1) or in ``half``s (i, i + rot_dims/2)
+  scores                 s = (q . k) * scale, then ``softcap`` * tanh(s / softcap) if given
+  visibility             key j for the query at p: j <= p and (p - j < window or j < keep_first); no window
+                         = all earlier keys.  Kept tokens keep their own positions.
+  ``sink``               one more term of score 0 and no value in the denominator:
+                         p_j = exp(s_j) / (1 + sum exp(s_j))
+  ``gate``               the heads' results times sigmoid(g), element by element, ahead of the output projection
+
+Keys are ``dim`` wide, values ``vdim``.  Keys (rotated) and values live in the paged cache; the last
+``taps - 1`` projected rows of a sequence live in its state slot, so a prompt may be cut anywhere.  Scores,
+softmax and the gate are float32 in either engine type.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..config.registry import register_part
+from ..kernels import ops
+from ..weights.loader import MATRIX, VECTOR, WeightSpec
+from .base import KVNeed, Part, RunInfo, StateNeed
+from .linear import Linear
+
+QUERY_TILE = 16     # tokens per query tile of the attention kernel
+
+
+@dataclass
+class QueryTiles:
+    """The step's query tiles of QUERY_TILE tokens and the entry of every row: int32 device tensors."""
+
+    tile_entry: torch.Tensor
+    tile_q0: torch.Tensor
+    n_tiles: int
+    row_entry: torch.Tensor
+
+
+def describe_query_tiles(layout, put) -> QueryTiles:
+    tile_entry, tile_q0 = [], []
+    for i in range(layout.n_entries):
+        for q0 in range(0, int(layout.q_len[i]), QUERY_TILE):
+            tile_entry.append(i), tile_q0.append(q0)
+    rows = np.repeat(np.arange(layout.n_entries), layout.q_len[:layout.n_entries])
+    return QueryTiles(put(tile_entry), put(tile_q0), len(tile_entry), put(rows))
+
+
+class WindowAttention(Part):
+    """params: ``hidden``, ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``conv`` (taps, 0 or 1 = none), ``rot_dims``,
+    ``rot_layout`` (``interleaved`` or ``half``), ``scale`` (None = ``dim^-1/2``), ``softcap`` (None = none),
+    ``window`` (None = all keys), ``keep_first``, ``sink``, ``gate``, ``name``.  Tensors
+    ``<prefix>.<name>.{q,k,v,g,o}`` and ``<prefix>.<name>.{q,k,v}.conv`` ``[channels, taps]``.
+    State: ``conv_tail`` float32 ``[taps - 1, channels of q, k and v]``.
+    Position: a pair ``(cos, sin)`` of float32 ``[N, rot_dims / 2]`` tensors."""
+
+    family = "mixer"
+    describe_key = "query_tiles"
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        p = params
+        self.hidden = int(p["hidden"])
+        self.heads, self.kv_heads = int(p["heads"]), int(p["kv_heads"])
+        self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
+        self.taps = int(p.get("conv") or 0)
+        self.rot_dims = int(p.get("rot_dims") or 0)
+        self.layout = ops.ROT_INTERLEAVED if p.get("rot_layout", "half") == "interleaved" else ops.ROT_HALF
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.dim)
+        self.softcap = float(p.get("softcap") or 0.0)
+        self.window = int(p.get("window") or 0)
+        self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
+        self.sink, self.gate = bool(p.get("sink")), bool(p.get("gate"))
+        if self.heads % self.kv_heads:
+            raise ValueError(f"heads {self.heads} is not a multiple of kv_heads {self.kv_heads}")
+        if self.rot_dims % 2 or self.rot_dims > self.dim:
+            raise ValueError(f"rot_dims {self.rot_dims} must be even and at most dim {self.dim}")
+        if not (1 <= self.dim <= 256 and 1 <= self.vdim <= 256):
+            raise ValueError("dim and vdim must be within 1..256")
+        if self.taps > 8:
+            raise ValueError("a convolution of more than 8 taps is not built")
+        self.qkvg: Linear = None
+        self.conv_w: Optional[torch.Tensor] = None
+        self.o: Linear = None
+
+    @classmethod
+    def _channels(cls, p) -> int:
+        return (int(p["heads"]) + int(p["kv_heads"])) * int(p["dim"]) + int(p["kv_heads"]) * int(p["vdim"])
+
+    @classmethod
+    def weight_specs(cls, params: Dict[str, Any], prefix: str) -> List[WeightSpec]:
+        h, nh, nkv, d, vd = (int(params[k]) for k in ("hidden", "heads", "kv_heads", "dim", "vdim"))
+        n = lambda leaf: cls.full_name(prefix, params, leaf)
+        rows = {"q": nh * d, "k": nkv * d, "v": nkv * vd}
+        specs = [WeightSpec(n(x), (r, h), MATRIX) for x, r in rows.items()]
+        taps = int(params.get("conv") or 0)
+        if taps > 1:
+            specs += [WeightSpec(n(f"{x}.conv"), (r, taps), VECTOR, std=0.5) for x, r in rows.items()]
+        if params.get("gate"):
+            specs.append(WeightSpec(n("g"), (nh * vd, h), MATRIX))
+        specs.append(WeightSpec(n("o"), (h, nh * vd), MATRIX))
+        return specs
+
+    @classmethod
+    def kv_need(cls, params: Dict[str, Any]) -> Optional[KVNeed]:
+        window = int(params.get("window") or 0) or None
+        return KVNeed.keys_and_values(int(params["kv_heads"]), int(params["dim"]), window,
+                                      value_dim=int(params["vdim"]), keep_first=int(params.get("keep_first") or 0))
+
+    @classmethod
+    def state_needs(cls, params: Dict[str, Any]) -> List[StateNeed]:
+        taps = int(params.get("conv") or 0)
+        return [StateNeed("conv_tail", (taps - 1, cls._channels(params)), torch.float32)] if taps > 1 else []
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
+        names = ["q", "k", "v"] + (["g"] if self.gate else [])
+        mats = [tensors.pop(n(x)) for x in names]
+        if len({m.dtype for m in mats}) > 1:
+            mats = [m.float() for m in mats]
+        self.qkvg = Linear(torch.cat(mats, dim=0))
+        del mats
+        if self.taps > 1:
+            self.conv_w = torch.cat([tensors.pop(n(f"{x}.conv")).float() for x in ("q", "k", "v")]).contiguous()
+        self.o = Linear(tensors.pop(n("o")))
+
+    def describe_step(self, layout, put) -> QueryTiles:
+        return describe_query_tiles(layout, put)
+
+    @property
+    def inner_width(self) -> int:
+        return self.heads * self.vdim
+
+    def inner(self, x: torch.Tensor, ctx, run: RunInfo, position, out: torch.Tensor = None) -> torch.Tensor:
+        """The gated heads ``[N, heads * vdim]`` that the output projection takes."""
+        n = x.shape[0]
+        step: QueryTiles = ctx.extras[self.describe_key]
+        if self.rot_dims:
+            if not (isinstance(position, (tuple, list)) and len(position) == 2 and 2 * position[0].shape[1] == self.rot_dims):
+                raise TypeError("window_attention takes its position as a pair (cos, sin) of [N, rot_dims / 2] float32 "
+                                "tensors; the layer's position encoding gave something else")
+            cos, sin = position
+        else:
+            cos = sin = torch.empty((n, 0), dtype=torch.float32, device=x.device)
+        g = run.kv_group
+        views, page_stride = ctx.kv.stream_views(g, run.kv_index)
+        k_layer, v_layer = views["k"], views["v"]
+        proj = self.qkvg.forward(x, out_dtype=torch.float32)            # float32 sums: they go on into the convolution and the rotation
+        q = torch.empty((n, self.heads * self.dim), dtype=x.dtype, device=x.device)
+        ops.conv_rope_kv_write(proj, self.conv_w, self.taps, run.states["conv_tail"] if self.taps > 1 else None,
+                               step.row_entry, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_slot, ctx.n_entries, cos, sin,
+                               self.layout, self.heads, self.kv_heads, self.dim, self.vdim, q, ctx.slot_maps[g],
+                               k_layer, v_layer, page_stride, ctx.page_size)
+        if out is None:
+            out = torch.empty((n, self.heads * self.vdim), dtype=x.dtype, device=x.device)
+        gate = proj[:, self._channels(self.params):] if self.gate else None
+        ops.attn_paged_options(q, q.stride(0), out, k_layer, v_layer, page_stride, ctx.page_size, ctx.block_tables[g],
+                               step.tile_entry, step.tile_q0, step.n_tiles, ctx.entry_q_start, ctx.entry_q_len,
+                               ctx.entry_ctx_start, self.heads, self.kv_heads, self.dim, self.scale, self.window,
+                               self.vdim, self.softcap, self.keep_first, self.sink, gate)
+        return out
+
+    def forward(self, x: torch.Tensor, ctx, run: RunInfo, position):
+        return self.o.forward(self.inner(x, ctx, run, position), allow_partials=True, f32_sums=True, out_dtype=torch.float32)
+
+
+register_part("mixer", "window_attention", WindowAttention)
