@@ -191,3 +191,90 @@ def load_kunonex_plain(folder: str):
         cfg = json.load(f)
     sf = SafetensorsFile(os.path.join(folder, "model.safetensors"))
     return cfg, {n: sf.tensor(n).double() for n in sf.names()}
+
+
+# ------------------------------------------------------------------ Pemorax
+def _px_left(heads, kv_heads, dim, vdim, conv=None, mask=None, rot=None, scale=None, softcap=None):
+    m = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim)
+    for k, v in (("conv", conv), ("mask", mask), ("rot", rot), ("scale", scale), ("softcap", softcap)):
+        if v is not None:
+            m[k] = v
+    return m
+
+
+def _px_right(heads, dim, vdim, decay, rot=None):
+    m = dict(heads=heads, dim=dim, vdim=vdim, decay=decay)
+    if rot is not None:
+        m["rot"] = rot
+    return m
+
+
+def _px_layer(left, right, mlp):
+    return dict(type="parallel", mixer=dict(left=left, right=right), mlp=mlp)
+
+
+_YARN = dict(factor=4.0, original=64, fast=16.0, slow=2.0)
+_MOE = lambda ff, experts, top: dict(kind="moe", expert=dict(ff=ff), router=dict(experts=experts, top=top))
+# Tiny Pemorax configurations that differ in every size and option.  A: dim != vdim on both sides, part of a head
+# rotates, scaled frequencies, a window of 20 that keeps 3, four taps, a decay of 1, experts 2 of 5, a layer
+# without feed-forward whose attention has no convolution, no window, no rotation and no cap.
+PX_A = dict(architecture="Pemorax", width=64, vocab=300, norm=dict(eps=1e-5), layers=[
+    _px_layer(_px_left(4, 2, 16, 24, conv=4, mask=dict(size=20, keep_first=3), rot=dict(dims=8, base=10000.0, scaling=_YARN),
+                       scale=0.3, softcap=8.0),
+              _px_right(3, 12, 20, [0.9, 0.97, 1.0], rot=dict(dims=12, base=5000.0)), dict(kind="dense", ff=96)),
+    _px_layer(_px_left(2, 2, 32, 32, conv=2, mask=dict(size=33, keep_first=0), rot=dict(dims=32, base=300.0)),
+              _px_right(1, 16, 8, [0.95], rot=dict(dims=4, base=100.0)), _MOE(40, 5, 2)),
+    _px_layer(_px_left(3, 1, 8, 4), _px_right(2, 8, 8, [0.5, 0.99]), None)])
+# B: sizes that are no multiple of 4 or 8 anywhere, a window shorter than a page, every expert chosen, one expert of three
+PX_B = dict(architecture="Pemorax", width=50, vocab=77, norm=dict(eps=3e-6), layers=[
+    _px_layer(_px_left(3, 3, 10, 6, conv=3, mask=dict(size=7, keep_first=1), rot=dict(dims=6, base=50.0), softcap=3.0),
+              _px_right(2, 6, 10, [0.8, 0.999], rot=dict(dims=6, base=1000.0)), _MOE(35, 3, 3)),
+    _px_layer(_px_left(5, 1, 6, 10, conv=8, mask=dict(size=40, keep_first=18), rot=dict(dims=2, base=20.0)),
+              _px_right(5, 10, 6, [0.7, 0.9, 0.95, 0.99, 0.995], rot=dict(dims=10, base=7.0)), _MOE(18, 3, 1)),
+    _px_layer(_px_left(1, 1, 14, 14, conv=2, mask=dict(size=64, keep_first=64)), _px_right(1, 14, 2, [0.96]), dict(kind="dense", ff=45))])
+# C: heads of 64 and of 128 (the sizes tensor-core kernels take), windows longer than several pages, many experts
+PX_C = dict(architecture="Pemorax", width=128, vocab=200, norm=dict(eps=1e-6), layers=[
+    _px_layer(_px_left(4, 2, 64, 64, conv=4, mask=dict(size=70, keep_first=5), rot=dict(dims=64, base=250000.0, scaling=_YARN),
+                       scale=0.125, softcap=30.0),
+              _px_right(2, 64, 64, [0.97, 0.999], rot=dict(dims=64, base=1e6)), _MOE(48, 12, 3)),
+    _px_layer(_px_left(2, 1, 128, 128, conv=2, mask=dict(size=100, keep_first=17), rot=dict(dims=64, base=10000.0), softcap=20.0),
+              _px_right(1, 128, 128, [0.99], rot=dict(dims=32, base=1e4)), dict(kind="dense", ff=160))])
+PX = {"A": PX_A, "B": PX_B, "C": PX_C}
+
+
+def pemorax_tensors(cfg: dict, seed: int, sharpen: float = 8.0):
+    """Random tensors (bfloat16 matrices) for a Pemorax configuration.  ``sharpen`` multiplies the attention's
+    query and key projections so that the softmax is peaked on single keys wherever they lie (with N(0, 0.02)
+    weights it is nearly uniform, and a lost key among hundreds or a missing sink would hide below the bfloat16
+    tolerance); the other projections are enlarged so that every branch carries weight in the sums."""
+    from inferflux_b200.config import load_config
+    from inferflux_b200.config.registry import build_spec
+    from inferflux_b200.engine.model import Model
+    from inferflux_b200.weights.random_init import random_tensors
+    config = load_config(json.loads(json.dumps(cfg)))
+    specs = Model(build_spec(config), torch.float32, "cpu").weight_specs()
+    tensors = random_tensors(specs, seed, torch.bfloat16, None, "cpu")
+    for name in tensors:
+        f = 1.0
+        if name.endswith((".left.q", ".left.k")):
+            f = sharpen
+        elif name.endswith((".right.q", ".right.k", ".right.v", ".left.v", ".g", ".o", ".up", ".down", ".gate")):
+            f = 4.0
+        elif name == "embed":
+            f = 20.0
+        if f != 1.0:
+            tensors[name] = (tensors[name].float() * f).to(tensors[name].dtype)
+    return config, tensors
+
+
+def make_pemorax_folder(cfg: dict, seed: int, folder: Optional[str] = None, **kw) -> str:
+    from inferflux_b200.weights.safetensors_io import write_safetensors
+    folder = folder or tempfile.mkdtemp(prefix="ifx_px_")
+    config, tensors = pemorax_tensors(cfg, seed, **kw)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    return folder
+
+
+load_plain_folder = load_kunonex_plain        # (config dict, float64 tensors) of any model folder

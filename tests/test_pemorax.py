@@ -1,0 +1,546 @@
+"""The Pemorax architecture against its plain restatement (plain_pemorax.py): every mechanism alone through its
+part and kernels, then whole models of three tiny configurations that differ in every size and option, stepped
+whole, token by token, in portions down to two tokens, in mixed batches over a pool so small that pages and state
+slots are used again, through bin/trace_run and through Engine.generate.  Weights are random; attention is
+sharpened so that single keys, far ones too, carry the result, and one test sets keys and queries by hand so that
+one score stands out just inside and just outside every edge."""
+from __future__ import annotations
+
+import copy
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import plain_pemorax as plain
+from helpers import PX, TOL, TraceProcess, make_pemorax_folder, pemorax_tensors, random_tokens
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+PTOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
+# Whole models.  float32: the largest difference as a fraction of the largest logit.  bfloat16: every sublayer
+# alone, fed the plain stream, is within 0.5 % (root mean square) of the plain result, sharp attention or not; each
+# layer passes on what came before about doubled, so behind three layers single logits are off by 4 to 11 % of the
+# largest while a position's logits as a whole stay close: the measure is a position's root-mean-square error over
+# the vocabulary as a fraction of the logits' root mean square.  (What a fault costs in float32: a window or a kept
+# count that is off by one moves the logits of these models by 4 to 99 % of the largest, a missing sink by 20 to 75 %.)
+# bfloat16 whole models keep the weights as drawn and test the path (cache type, few-row and many-row products,
+# the captured step); edges, far keys and the sink are tested sharp in bfloat16 on the parts alone.
+MTOL = {torch.float32: 5e-5, torch.bfloat16: 8e-2}
+SHARPEN = {torch.float32: 8.0, torch.bfloat16: 1.0, "float32": 8.0, "bfloat16": 1.0}
+NAME = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
+gpu = pytest.mark.gpu
+
+
+def _rel(got, want):
+    got, want = torch.as_tensor(got).double().cpu(), torch.as_tensor(want).double().cpu()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+def _row_err(got, want):
+    """Per position: the root mean square over the vocabulary of the difference (its mean taken off), as a fraction
+    of the root mean square of all the plain logits; the largest over the positions."""
+    got, want = torch.as_tensor(got).double().cpu(), torch.as_tensor(want).double().cpu()
+    d = got - want
+    d = d - d.mean(-1, keepdim=True)
+    return float(d.pow(2).mean(-1).sqrt().max() / (want - want.mean(-1, keepdim=True)).pow(2).mean().sqrt())
+
+
+def _model_ok(got, want, dtype):
+    """Whole models: float32 by the largest difference; bfloat16 by :func:`_row_err` (see MTOL)."""
+    if dtype in (torch.float32, "float32"):
+        return _rel(got, want) < MTOL[torch.float32]
+    return _row_err(got, want) < MTOL[torch.bfloat16]
+
+
+def _rand(shape, seed, scale=1.0):
+    return torch.randn(shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+def _dense(y):
+    from inferflux_b200.parts.base import PartialSums
+    return y.tensor.sum(0) if isinstance(y, PartialSums) else y.float()
+
+
+def _for_dtype(cfg, dtype):
+    """The configuration a whole-model test runs in this element type.  Which experts a token takes is a
+    discrete choice: in bfloat16 the stream differs from the plain one by roundings that can turn a close call the
+    other way, and the logits then differ entirely.  So bfloat16 models take every expert (``top = experts``: the
+    weights still vary with the token, the sort and the tiles are the same); the choice itself is tested in
+    bfloat16 on the part alone, with close calls left out, and in whole models in float32."""
+    if dtype in (torch.float32, "float32"):
+        return cfg
+    cfg = copy.deepcopy(cfg)
+    for layer in cfg["layers"]:
+        if layer["mlp"] and layer["mlp"]["kind"] == "moe":
+            layer["mlp"]["router"]["top"] = layer["mlp"]["router"]["experts"]
+    return cfg
+
+
+# ------------------------------------------------------------------ CPU: configuration, spec, cache plan
+def test_config_is_read_from_its_own_keys():
+    from inferflux_b200.config import ConfigError, PemoraxConfig, build_spec, load_config
+    cfg = load_config(copy.deepcopy(PX["A"]))
+    assert isinstance(cfg, PemoraxConfig) and cfg.width == 64 and cfg.vocab_size == 300 and cfg.norm_eps == 1e-5
+    left, right = cfg.layers[0].mixer["left"], cfg.layers[0].mixer["right"]
+    assert (left["heads"], left["kv_heads"], left["dim"], left["vdim"], left["conv"]) == (4, 2, 16, 24, 4)
+    assert left["mask"] == {"size": 20, "keep_first": 3} and left["softcap"] == 8.0 and left["rot"]["scaling"]["factor"] == 4.0
+    assert right["decay"] == [0.9, 0.97, 1.0] and right["rot"] == {"dims": 12, "base": 5000.0, "scaling": None}
+    bare = cfg.layers[2].mixer["left"]
+    assert bare["conv"] == 0 and bare["mask"] is None and bare["rot"]["dims"] == 0 and bare["softcap"] is None
+    assert bare["scale"] == 8 ** -0.5                                      # absent: one over the root of dim
+    assert cfg.layers[1].mlp == {"kind": "moe", "ff": 40, "experts": 5, "top": 2} and cfg.layers[2].mlp is None
+    assert load_config(cfg.to_dict()) == cfg                                # what it writes, it reads back
+    spec = build_spec(cfg)
+    # four distinct sets of rotary parameters (the third layer rotates nothing): four tables
+    assert sorted(spec.positions) == ["rot0", "rot1", "rot2", "rot3"]
+    assert [l.arrangement for l in spec.layers] == ["sandwich"] * 3 and "feed_forward" not in spec.layers[2].parts
+    assert spec.layers[1].parts["feed_forward"].kind == "routed_experts"
+    branches = spec.layers[0].parts["mixer"].params["branches"]
+    assert [b["kind"] for b in branches] == ["window_attention", "retention"] and branches[0]["position"] == "rot0"
+    same = copy.deepcopy(PX["A"])
+    same["layers"][1]["mixer"]["right"]["rot"] = dict(dims=12, base=5000.0)          # the same table as layer 0's
+    assert len(build_spec(load_config(same)).positions) == 3
+    for breaker, text in [(lambda d: d["layers"][0].update(type="serial"), "type"), (lambda d: d.pop("width"), "width"),
+                          (lambda d: d["layers"][0]["mixer"]["left"].pop("dim"), "dim"),
+                          (lambda d: d["layers"][0]["mixer"]["right"].update(decay=[0.9]), "decay"),
+                          (lambda d: d["layers"][0]["mixer"]["left"]["rot"].update(dims=18), "rot.dims"),
+                          (lambda d: d["layers"][0]["mixer"]["left"].update(kv_heads=3), "kv_heads"),
+                          (lambda d: d["layers"][1]["mlp"]["router"].update(top=6), "top"),
+                          (lambda d: d["norm"].pop("eps"), "eps"), (lambda d: d["layers"][0]["mlp"].update(kind="glu"), "kind")]:
+        bad = copy.deepcopy(PX["A"])
+        breaker(bad)
+        with pytest.raises(ConfigError, match=text):
+            load_config(bad)
+
+
+def test_cache_and_state_plan():
+    from inferflux_b200.config import build_spec, load_config
+    from inferflux_b200.engine import Model
+    model = Model(build_spec(load_config(copy.deepcopy(PX["A"]))), torch.float32, "cpu")
+    names = {w.name: tuple(w.shape) for w in model.weight_specs()}
+    assert names["embed"] == (300, 64) and names["head"] == (300, 64) and names["final.norm"] == (64,)
+    assert names["l0.mix.left.q"] == (64, 64) and names["l0.mix.left.k"] == (32, 64) and names["l0.mix.left.v"] == (48, 64)
+    assert names["l0.mix.left.g"] == (96, 64) and names["l0.mix.left.o"] == (64, 96) and names["l0.mix.left.v.conv"] == (48, 4)
+    assert names["l0.mix.right.v"] == (60, 64) and names["l0.mix.right.out"] == (64,) and names["l0.norm2b"] == (64,)
+    assert names["l1.mlp.router"] == (5, 64) and names["l1.mlp.router.b"] == (5,) and names["l1.mlp.e4.down"] == (64, 40)
+    assert "l2.mix.left.q.conv" not in names and "l2.norm2" not in names and "l2.mlp.up" not in names
+    # three cache groups: keys and values of different widths and windows; the window's kept tokens are part of the need
+    needs = [(n.streams[0].width, n.streams[1].width, n.window, n.keep_first) for n in model.kv_needs]
+    assert needs == [(16, 24, 20, 3), (32, 32, 33, 0), (8, 4, None, 0)]
+    states = [{s.name: tuple(s.shape) for s in per_run} for per_run in model.state_needs]
+    assert states[0] == {"conv_tail": (3, 64 + 32 + 48), "retention": (3, 12, 20)}
+    assert states[2] == {"retention": (2, 8, 8)}                           # no convolution, no tail
+
+
+def test_kept_first_pages_stay_behind_the_window():
+    from inferflux_b200.cache import KVCacheManager
+    from inferflux_b200.parts.base import KVNeed
+    need = KVNeed.keys_and_values(1, 8, window=10, value_dim=4, keep_first=5)       # 5 kept tokens: the first two pages of 4
+    kv = KVCacheManager([need], [12], 4)
+    kv.add_request("a")
+    kv.reserve("a", 30), kv.advance("a", 30)
+    table = kv.block_table("a", 0)
+    # keys from 30 - 10 + 1 = 21 on are needed: blocks 0 and 1 (kept) and 5.. stay, 2..4 went back to the pool
+    assert [b >= 0 for b in table] == [True, True, False, False, False, True, True, True]
+    assert kv.num_free(0) == 12 - 5
+    kv.check()
+    kv.free_request("a")
+    assert kv.num_free(0) == 12
+
+
+def test_plain_carry_over_and_routing():
+    """The plain implementation's own consistency: a sequence cut in two, tail and state handed over."""
+    u, w = _rand((11, 6), 1).double(), _rand((6, 4), 2).double()
+    whole, _ = plain.short_conv(u, w)
+    a, tail = plain.short_conv(u[:2], w)                     # shorter than the taps: the tail is part old, part new
+    b, tail = plain.short_conv(u[2:3], w, tail)
+    c, _ = plain.short_conv(u[3:], w, tail)
+    assert torch.allclose(torch.cat([a, b, c]), whole)
+    assert torch.allclose(whole[0], w[:, 3] * u[0]) and torch.allclose(whole[1], w[:, 3] * u[1] + w[:, 2] * u[0])
+    q, k, v = _rand((9, 2, 5), 3).double(), _rand((9, 2, 5), 4).double(), _rand((9, 2, 3), 5).double()
+    o, s = plain.retention_scan(q, k, v, [0.9, 1.0])
+    o1, s1 = plain.retention_scan(q[:4], k[:4], v[:4], [0.9, 1.0])
+    o2, s2 = plain.retention_scan(q[4:], k[4:], v[4:], [0.9, 1.0], s1)
+    assert torch.allclose(torch.cat([o1, o2]), o) and torch.allclose(s2, s)
+    # as a sum over earlier tokens: o_t = sum_j decay^(t-j) (q_t . k_j) v_j
+    direct = sum(0.9 ** (8 - j) * (q[8, 0] @ k[j, 0]) * v[j, 0] for j in range(9))
+    assert torch.allclose(o[8, 0], direct)
+    ids, wts = plain.route(torch.tensor([[1.0, 3.0, 3.0, -1.0]], dtype=torch.float64), 2)
+    assert ids.tolist() == [[1, 2]] and torch.allclose(wts, torch.tensor([[0.5, 0.5]], dtype=torch.float64))
+    see = plain.visible(3, 10, dict(size=4, keep_first=2))
+    assert see[0].nonzero().flatten().tolist() == [0, 1, 7, 8, 9, 10] and see[2].nonzero().flatten().tolist() == [0, 1, 9, 10, 11, 12]
+    f, mag = plain.frequencies(dict(dims=8, base=10000.0, scaling=dict(factor=4.0, original=64, fast=16.0, slow=2.0)))
+    assert abs(mag - (0.1 * np.log(4.0) + 1)) < 1e-12 and abs(float(f[0]) - 1.0) < 1e-12 and abs(float(f[3]) - 1e-3 / 4) < 1e-12
+
+
+# ------------------------------------------------------------------ GPU: the mechanisms alone
+def _runner_for(cfg, dtype, seed, tokens=512, tensors=None, **kw):
+    from inferflux_b200.config import EngineConfig
+    from inferflux_b200.config.registry import build_spec
+    from inferflux_b200.engine import Model, StepRunner
+    config, made = pemorax_tensors(cfg, seed, **kw)
+    tensors = tensors or made
+    model = Model(build_spec(config), dtype, DEV)
+    plain_w = {k: v.double() for k, v in tensors.items()}
+    model.load({k: (v.to(dtype) if v.dim() > 1 else v.float()).to(DEV) for k, v in tensors.items()})
+    runner = StepRunner(model, EngineConfig(dtype=NAME[dtype], kv_cache_tokens=tokens, max_seqs=4))
+    return model, runner, plain_w
+
+
+def _branch_in_portions(model, runner, which, x, portions, dtype):
+    """Call one branch of layer 0's mixer alone on rows cut into portions of one request."""
+    from inferflux_b200.engine import StepEntry
+    info = model.runs[0]
+    pair = model.blocks[0].mixer
+    branch, spec = pair.mixers[which], pair.branch_specs[which]
+    outs, pos = [], 0
+    for n in portions:
+        ctx = runner.build_context([StepEntry("r", [1] * n, [])])
+        for name, part in model.positions.items():
+            ctx.position_tables[name] = part.prepare(ctx)
+        position = ctx.position_tables.get(spec["position"]) if spec["position"] else None
+        outs.append(_dense(branch.forward(x[pos:pos + n].to(dtype).to(DEV), ctx, info, position)))
+        runner.kv.advance("r", n)
+        pos += n
+    runner.end("r")
+    return torch.cat(outs)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [50, 64, 1000, 5000])
+def test_norm_chain_alone(dtype, hidden):
+    """Two normed branches, their mean, the norm behind, the sum, the norm ahead; slices that are added first;
+    picked rows that leave the stream untouched."""
+    from inferflux_b200.parts import RMSNorm
+    from inferflux_b200.parts.base import BranchMean, NormedDelta, PartialSums
+    eps = 3e-6
+    part = RMSNorm(dict(weight_name="n", hidden=hidden, eps=eps), "l", dtype, DEV)
+    assert [w.name for w in RMSNorm.weight_specs(part.params, "l")] == ["l.n"]
+    ws = [1 + _rand((hidden,), 10 + i, 0.2) for i in range(4)]
+    part.load({"l.n": ws[3].to(DEV)})
+    res, a, b = _rand((7, hidden), 1, 3.0).to(DEV), _rand((3, 7, hidden), 2).to(DEV), _rand((7, hidden), 3, 5.0).to(DEV)
+    y = 0.5 * (plain.rms_norm(a.cpu().double().sum(0), ws[0].double(), eps) + plain.rms_norm(b.cpu().double(), ws[1].double(), eps))
+    want_res = res.cpu().double() + plain.rms_norm(y, ws[2].double(), eps)
+    want = plain.rms_norm(want_res, ws[3].double(), eps)
+    delta = NormedDelta(BranchMean([(PartialSums(a), ws[0].to(DEV)), (b, ws[1].to(DEV))], eps), ws[2].to(DEV), eps)
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+    before = res.clone()
+    picked = part.forward(res, delta, rows=rows)
+    assert torch.equal(res, before) and _rel(picked, want[[5, 0, 5]]) < PTOL[dtype]
+    out = part.forward(res, delta)
+    assert _rel(out, want) < PTOL[dtype] and _rel(res, want_res) < 1e-6
+    res2 = before.clone()                                        # one branch only: norm behind, sum, norm ahead
+    out2 = part.forward(res2, NormedDelta(b, ws[2].to(DEV), eps))
+    want2 = before.cpu().double() + plain.rms_norm(b.cpu().double(), ws[2].double(), eps)
+    assert _rel(res2, want2) < 1e-6 and _rel(out2, plain.rms_norm(want2, ws[3].double(), eps)) < PTOL[dtype]
+
+
+@gpu
+@pytest.mark.parametrize("layout", ["interleaved", "half"])
+def test_rotation_alone(layout):
+    """Part of a head rotates, by scaled frequencies, at positions far out; the rest passes unchanged."""
+    from inferflux_b200.kernels import ops
+    from inferflux_b200.parts.position import RotaryHalf
+    rot = dict(dims=12, base=3000.0, scaling=dict(factor=8.0, original=40, fast=8.0, slow=1.0))
+    part = RotaryHalf(dict(rotary_dim=12, theta=3000.0, scaling=rot["scaling"]), "", torch.float32, DEV)
+    pos = torch.tensor([0, 1, 2, 63, 64, 1000, 123456], dtype=torch.int32, device=DEV)
+
+    class Ctx:
+        n_tokens, positions, device = 7, pos, DEV
+    cos, sin = part.prepare(Ctx)
+    x = _rand((7, 5 + 3 * 20 + 2), 4).to(DEV)
+    want = x.cpu().double().clone()
+    want[:, 5:65] = plain.rotate(want[:, 5:65].reshape(7, 3, 20), pos.cpu(), rot, layout == "interleaved").reshape(7, 60)
+    ops.rotate_heads(x, 5, 3, 20, cos, sin, ops.ROT_INTERLEAVED if layout == "interleaved" else ops.ROT_HALF)
+    assert _rel(x, want) < 2e-6 and torch.equal(x[:, :5].cpu().double(), want[:, :5])
+
+
+@gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_edges_with_one_score_that_stands_out(dtype):
+    """210 tokens, a window of 40 that keeps the first 5, pages of 16.  Head 0's query is the token's first 16
+    numbers and its key the next 16, nothing rotates and nothing is convolved; each of the last eight tokens gets
+    a query that matches the key of one chosen earlier token and no other: the last one inside its window, the
+    first one outside, the last kept token, the first not kept, a page's last and first token inside the window,
+    the very first token, and itself.  A visible target takes the whole weight, an invisible one leaves the sink
+    with it; a window, a kept count or a page's edge that is off by one changes the result entirely.  The first
+    two of the eight queries come inside a portion, the others as single tokens."""
+    n, dim, wn, keep = 210, 16, 40, 5
+    left = dict(heads=2, kv_heads=1, dim=dim, vdim=12, mask=dict(size=wn, keep_first=keep), scale=1.0)
+    cfg = dict(PX["A"], layers=[dict(type="parallel", mixer=dict(left=left, right=PX["A"]["layers"][2]["mixer"]["right"]), mlp=None)])
+    _, tensors = pemorax_tensors(cfg, 21)
+    eye = torch.eye(dim)
+    tensors["l0.mix.left.q"] = torch.cat([torch.cat([eye, torch.zeros(dim, 48)], 1), _rand((dim, 64), 22, 0.05)]).to(torch.bfloat16)
+    tensors["l0.mix.left.k"] = torch.cat([torch.zeros(dim, dim), eye, torch.zeros(dim, 32)], 1).to(torch.bfloat16)
+    model, runner, w = _runner_for(cfg, dtype, 21, tensors=tensors)
+    x = _rand((n, 64), 23, 0.3).to(torch.bfloat16).float()
+    x[:, :2 * dim] *= 0.1                                        # quiet queries and keys, but for the chosen pairs
+    first_q = n - 8
+    targets = [p - off if off is not None else t for p, (off, t) in zip(range(first_q, n), [
+        (wn - 1, None), (wn, None), (None, keep - 1), (None, keep), (None, 191), (None, 192), (None, 0), (0, None)])]
+    for q, t in zip(range(first_q, n), targets):
+        u = torch.zeros(dim)
+        u[(q - first_q) % dim] = 1.0                             # a direction of its own for every pair
+        x[t, dim:2 * dim] = 4.0 * u
+        x[q, :dim] = 4.0 * u
+    m = plain.fill_left(left)
+    want = plain.left_mixer(x.double(), w, "l0.mix.left", m)
+    seen = [True, False, True, False, True, True, True, True]
+    for q, t, vis in zip(range(first_q, n), targets, seen):      # the plain result does rest on these single keys
+        other = x.clone()
+        other[t, dim:2 * dim] = 0.0
+        moved = plain.left_mixer(other.double(), w, "l0.mix.left", m)[q]
+        assert (_rel(moved, want[q]) > 0.2) == vis, (q, t)
+    got = _branch_in_portions(model, runner, 0, x, [150, 54] + [1] * 6, dtype)
+    assert _rel(got, want) < PTOL[dtype]
+    wider = dict(m, mask=dict(size=wn + 1, keep_first=keep + 1))  # the two invisible targets, made visible, would show
+    shown = plain.left_mixer(x.double(), w, "l0.mix.left", wider)
+    assert _rel(shown[first_q + 1], want[first_q + 1]) > 0.2 and _rel(shown[first_q + 3], want[first_q + 3]) > 0.2
+
+
+@gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,layer", [("A", 0), ("A", 1), ("A", 2), ("B", 0), ("B", 1), ("B", 2), ("C", 0), ("C", 1)])
+def test_attention_branch_alone(dtype, name, layer):
+    """Portions that start and end inside pages and inside the convolution's reach (one and two tokens against up
+    to eight taps), single tokens across page borders and past the window; then the slot and the pages again."""
+    cfg = dict(PX[name], layers=[PX[name]["layers"][layer]])
+    model, runner, w = _runner_for(cfg, dtype, 30 + layer, tokens=256)
+    portions = [21, 1, 2, 1, 1, 10, 45, 1, 1, 2, 16, 1, 40]
+    x = _rand((sum(portions), cfg["width"]), 31).to(dtype)
+    m = plain.fill_left(cfg["layers"][0]["mixer"]["left"])
+    want = plain.left_mixer(x.double(), w, "l0.mix.left", m)
+    got = _branch_in_portions(model, runner, 0, x, portions, dtype)
+    assert _rel(got, want) < PTOL[dtype]
+    again = _branch_in_portions(model, runner, 0, x[:9], [2, 7], dtype)
+    assert _rel(again, want[:9]) < PTOL[dtype]
+    runner.kv.check()
+
+
+@gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,layer", [("A", 0), ("A", 1), ("A", 2), ("B", 1), ("B", 2), ("C", 0), ("C", 1)])
+def test_retention_branch_alone(dtype, name, layer):
+    """A portion of several segments, single tokens, two tokens, a portion that ends on a segment's edge; decays of
+    1 and of 0.5; the state goes through the request's slot, which the next request finds zeroed."""
+    cfg = dict(PX[name], layers=[PX[name]["layers"][layer]])
+    model, runner, w = _runner_for(cfg, dtype, 40 + layer, tokens=512)
+    portions = [150, 1, 1, 2, 64, 7, 1, 33]
+    x = _rand((sum(portions), cfg["width"]), 41).to(dtype)
+    m = plain.fill_right(cfg["layers"][0]["mixer"]["right"])
+    want = plain.right_mixer(x.double(), w, "l0.mix.right", m, cfg["norm"]["eps"])
+    got = _branch_in_portions(model, runner, 1, x, portions, dtype)
+    assert _rel(got, want) < PTOL[dtype]
+    again = _branch_in_portions(model, runner, 1, x[:10], [10], dtype)
+    assert _rel(again, want[:10]) < PTOL[dtype]
+
+
+@gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,ff,experts,top,rows", [(64, 40, 5, 2, 3), (64, 40, 5, 2, 300), (50, 35, 3, 3, 70), (50, 18, 3, 1, 5),
+                                                        (128, 48, 12, 3, 1), (96, 200, 40, 8, 130)])
+def test_routed_experts_alone(dtype, hidden, ff, experts, top, rows):
+    """Few rows (short tiles) and many (tiles of 64, experts with more than one tile and with none), one expert a
+    token and every expert; rows whose choice rests on a close call are left out of the comparison."""
+    from inferflux_b200.parts.feed_forward import RoutedExperts
+    params = dict(name="mlp", hidden=hidden, intermediate=ff, experts=experts, top=top)
+    part = RoutedExperts(params, "l0", dtype, DEV)
+    w = {s.name: (_rand(s.shape, 50 + i, 0.5 if "router" in s.name else 0.15)).to(torch.bfloat16).float()
+         for i, s in enumerate(RoutedExperts.weight_specs(params, "l0"))}
+    part.load({k: (v.to(dtype) if v.dim() > 1 else v.float()).to(DEV) for k, v in w.items()})
+    x = _rand((rows, hidden), 51).to(dtype)
+    w64 = {k: v.double() for k, v in w.items()}
+    mlp = dict(router=dict(experts=experts, top=top))
+    want = plain.routed_ff(x.double(), w64, "l0.mlp", mlp)
+    z = x.double() @ w64["l0.mlp.router"].T + w64["l0.mlp.router.b"]
+    srt = torch.sort(z, dim=-1, descending=True).values
+    clear = torch.ones(rows, dtype=torch.bool) if top == experts else (srt[:, top - 1] - srt[:, top]) > 0.05
+    got = _dense(part.forward(x.to(DEV), None)).cpu()
+    assert clear.sum() >= rows * 0.7 and _rel(got[clear], want[clear]) < PTOL[dtype]
+
+
+@gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,ff,rows", [(64, 96, 3), (50, 45, 40), (128, 160, 300)])
+def test_gelu_feed_forward_alone(dtype, hidden, ff, rows):
+    from inferflux_b200.parts.feed_forward import GeluMLP
+    params = dict(name="mlp", hidden=hidden, intermediate=ff)
+    part = GeluMLP(params, "l0", dtype, DEV)
+    w = {"l0.mlp.up": _rand((ff, hidden), 60, 0.3).to(torch.bfloat16).float(), "l0.mlp.down": _rand((hidden, ff), 61, 0.3).to(torch.bfloat16).float()}
+    part.load({k: v.to(dtype).to(DEV) for k, v in w.items()})
+    x = _rand((rows, hidden), 62, 2.0).to(dtype)
+    want = plain.dense_ff(x.double(), {k: v.double() for k, v in w.items()}, "l0.mlp")
+    assert _rel(_dense(part.forward(x.to(DEV), None)), want) < PTOL[dtype]
+    z = torch.tensor([-3.0, -1.0, 0.0, 0.5, 2.0], dtype=torch.float64)      # the tanh form, not the erf form
+    assert torch.allclose(plain.gelu_tanh(z), torch.nn.functional.gelu(z, approximate="tanh"))
+
+
+# ------------------------------------------------------------------ GPU: whole models through the step function
+def _logits_in_steps(runner, rid, toks, sizes):
+    from inferflux_b200.engine import StepEntry
+    outs, pos, k = [], 0, 0
+    while pos < len(toks):
+        n = min(sizes[k % len(sizes)], len(toks) - pos)
+        outs.append(runner.step([StepEntry(rid, toks[pos:pos + n], list(range(n)))]).clone())
+        pos, k = pos + n, k + 1
+    runner.end(rid)
+    return torch.cat(outs)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_model_whole_one_by_one_and_in_portions(dtype, name):
+    """The logits at every position for three ways of cutting the same prompt, and the stream after every layer
+    for the whole prompt."""
+    cfg = _for_dtype(PX[name], dtype)
+    model, runner, w = _runner_for(cfg, dtype, ord(name), tokens=1024, sharpen=SHARPEN[dtype])
+    toks = random_tokens(cfg["vocab"], 150, 31)
+    want = plain.forward(cfg, w, toks)
+    whole = _logits_in_steps(runner, "w", toks, [150])
+    assert _model_ok(whole, want, dtype)
+    ones = _logits_in_steps(runner, "o", toks[:90], [1])              # the captured decode graph after three steps
+    assert runner.graph_replays > 0 and _model_ok(ones, want[:90], dtype)
+    cut = _logits_in_steps(runner, "c", toks, [2, 3, 17, 1, 16, 5, 32, 2, 15, 64, 2])
+    assert _model_ok(cut, want, dtype)
+    if dtype == torch.float32:
+        assert _rel(cut, whole) < 1e-5 and _rel(ones, whole[:90]) < 1e-5
+    runner.kv.check(), runner.slots.check()
+
+
+@gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_batches_of_unequal_requests_and_reused_slots(dtype, name):
+    """Four requests of unequal length, portions beside single tokens, against each alone; then four more in
+    the slots and pages the first ones gave back."""
+    from inferflux_b200.engine import StepEntry
+    cfg = _for_dtype(PX[name], dtype)
+    model, runner, w = _runner_for(cfg, dtype, 41, tokens=4 * 128, sharpen=SHARPEN[dtype])
+    rng = random.Random(3)
+    for round_ in range(2):
+        lens = [97, 5, 64, 33] if round_ == 0 else [31, 120, 2, 70]
+        reqs = {f"r{round_}{i}": random_tokens(cfg["vocab"], n, 500 + 100 * round_ + 10 * i) for i, n in enumerate(lens)}
+        want = {r: plain.forward(cfg, w, t) for r, t in reqs.items()}
+        alone = {}
+        for r, t in reqs.items():                                  # each alone, its whole prompt in one step
+            alone[r] = runner.step([StepEntry("alone", t, list(range(len(t))))]).clone()
+            runner.end("alone")
+        at, got = {r: 0 for r in reqs}, {r: [] for r in reqs}
+        while any(at[r] < len(reqs[r]) for r in reqs):
+            entries = []
+            for r, t in reqs.items():
+                left = len(t) - at[r]
+                if left == 0 or (rng.random() < 0.2 and len(entries)):
+                    continue
+                n = 1 if left <= 6 else min(left - 6, rng.choice([1, 2, 3, 16, 29]))
+                entries.append(StepEntry(r, t[at[r]:at[r] + n], list(range(n))))
+            logits = runner.step(entries)
+            row = 0
+            for e in entries:
+                got[e.rid].append(logits[row:row + len(e.tokens)].clone())
+                row += len(e.tokens)
+                at[e.rid] += len(e.tokens)
+        for r in reqs:
+            # against the same request alone the batch may differ by rounding only (bfloat16: few-row and many-row
+            # products round differently); against the plain result as whole models do, with room for a short request
+            assert _rel(torch.cat(got[r]), alone[r]) < (1e-5 if dtype == torch.float32 else 1e-2), r
+            if dtype == torch.float32:
+                assert _model_ok(torch.cat(got[r]), want[r], dtype), r
+            else:
+                assert _row_err(torch.cat(got[r]), want[r]) < 2 * MTOL[dtype], r
+            runner.end(r)
+        runner.kv.check(), runner.slots.check()
+    assert all(p.reuses > 0 for p in runner.kv.pools)
+
+
+@gpu
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_decoding_past_the_window(name):
+    """300 tokens at once, then 200 one by one through the captured graph: the windows (7 to 40 tokens) pass over
+    decoded tokens many times, pages behind them go back to the pool and come again, kept first tokens stay."""
+    cfg = PX[name]
+    model, runner, w = _runner_for(cfg, torch.float32, 51, tokens=512)
+    toks = random_tokens(cfg["vocab"], 500, 52)
+    want = plain.forward(cfg, w, toks)
+    got = _logits_in_steps(runner, "d", toks, [300] + [1] * 200)
+    assert runner.graph_replays >= 190 and _rel(got, want) < 5e-5
+    assert runner.kv.pools[0].reuses > 0
+
+
+# ------------------------------------------------------------------ GPU: bin/trace_run and Engine.generate
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_trace_replay_mixed_with_page_and_slot_reuse(name, dtype):
+    """The command-line replay: the config.json picks the architecture; four state slots, a pool of the four
+    longest requests; every request twice, so pages and slots turn over."""
+    from helpers import load_plain_folder as load_plain
+    cfg = _for_dtype(PX[name], dtype)
+    folder = make_pemorax_folder(cfg, seed=60 + ord(name), sharpen=SHARPEN[dtype])
+    pcfg, w = load_plain(folder)
+    lengths = [70, 33, 5, 130, 64, 97, 1]
+    requests = [random_tokens(cfg["vocab"], n, 1000 + 50 * i) for i, n in enumerate(lengths)]
+    refs = [plain.forward(pcfg, w, r).numpy() for r in requests]
+    pool = sum((n + 63) // 64 * 64 for n in sorted(lengths)[-4:])
+    proc = TraceProcess(folder, dtype, pool)
+    rng = random.Random(7)
+    waiting = [(f"m{j}_{i}", i) for j, i in enumerate(list(range(len(requests))) * 2)]
+    live, worst = {}, 0.0
+    while waiting or live:
+        while waiting and len(live) < 4:
+            rid, i = waiting.pop(0)
+            live[rid] = [i, 0]
+        entries, ends, checks = [], [], []
+        for rid, (i, pos) in list(live.items()):
+            toks = requests[i]
+            if rng.random() < 0.15 and len(live) > 1:
+                continue
+            left = len(toks) - pos
+            n = 1 if left <= 20 else min(left - 20, rng.choice([2, 3, 7, 16, 29, 48]))
+            want = list(range(n)) if n <= 3 else sorted(rng.sample(range(n), 3))
+            entries.append(dict(id=rid, tokens=toks[pos:pos + n], want=want))
+            checks.append((i, pos, want))
+            live[rid][1] = pos + n
+            if pos + n == len(toks):
+                ends.append(rid)
+                del live[rid]
+        if not entries:
+            continue
+        got = proc.step(entries, end=ends)
+        row = 0
+        for i, pos, want in checks:
+            for p in want:
+                err = np.abs(got[row].astype(np.float64) - refs[i][pos + p]).max() / np.abs(refs[i]).max()
+                worst = max(worst, err)
+                row += 1
+    stats = proc.stats()
+    assert proc.close() == 0
+    assert worst <= MTOL[{'float32': torch.float32, 'bfloat16': torch.bfloat16}[dtype]], worst
+    assert all(u > 0 for u in stats["page_reuses"]) and stats["pages_free"] == stats["pages_total"]
+
+
+@gpu
+def test_greedy_generation_through_the_engine():
+    """Engine.from_pretrained picks the architecture by config.json; the scheduler cuts prompts into portions of
+    16 and batches them with decoding requests; float32 greedy continuations equal the plain ones."""
+    from helpers import load_plain_folder as load_plain
+    from inferflux_b200 import Engine, SamplingParams
+    cfg = PX["A"]
+    folder = make_pemorax_folder(cfg, seed=71)
+    pcfg, w = load_plain(folder)
+    prompts = [random_tokens(cfg["vocab"], n, 80 + n) for n in (5, 41, 17, 70, 3)]
+
+    def plain_greedy(p, n):
+        seq = list(p)
+        for _ in range(n):
+            seq.append(int(plain.forward(pcfg, w, seq)[-1].argmax()))
+        return seq[len(p):]
+
+    want = [plain_greedy(p, 12) for p in prompts]
+    eng = Engine.from_pretrained(folder, dtype="float32", kv_cache_tokens=512, max_seqs=4, chunked_prefill_tokens=16)
+    got = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    assert [g.tokens for g in got] == want
