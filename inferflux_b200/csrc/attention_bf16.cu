@@ -145,13 +145,32 @@ struct AttnMeta {
   const int* entry_q_start; const int* entry_q_len; const int* entry_ctx_start;
 };
 
+// What newer attention designs add to the prompt kernel (all off for plain attention): a cap on the scores,
+// s <- cap * tanh(s / cap); first tokens that stay visible behind the window; a sink (one more term exp(0) in
+// the softmax's denominator, without a value); an output gate (the result times the sigmoid of float32 sums
+// given beside it, [parts][N][gate_stride], first n_heads * HD columns).
+struct PrefillOptions {
+  float softcap;
+  int keep_first;
+  int sink;
+  const float* gate; int gate_parts; long long gate_part_stride; int gate_stride;
+};
+
+// tanh from one exponential: (e^2x - 1) / (e^2x + 1), the argument held where e^2x neither overflows nor
+// rounds the result away from +-1 (errors of a few 1e-7 of the cap)
+__device__ __forceinline__ float tanh_exp(float x) {
+  x = fminf(fmaxf(x, -15.0f), 15.0f);
+  const float t = fast_exp2(x * (2.0f * LOG2E));
+  return __fdividef(t - 1.0f, t + 1.0f);
+}
+
 // ------------------------------------------------------------------ prompts
 // One block: 64 consecutive new tokens of one entry (16 per warp), one head.
 template <int HD>
 __global__ void __launch_bounds__(128)
 attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                          PagedKV kv, AttnMeta m, const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
-                         int n_heads, int n_kv, float scale, int window) {
+                         int n_heads, int n_kv, float scale, int window, PrefillOptions opt) {
   pdl_enter();
   constexpr int BQ = 64, BK = 64, KS = HD / 16, DT = HD / 8;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -190,16 +209,26 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   float o[DT][4];
 #pragma unroll
   for (int d = 0; d < DT; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f; }
-  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.0f, 0.0f};
-  const float sl2 = scale * LOG2E;
+  // a sink is a key of score 0 without a value: the running maximum starts at 0 and the sum at exp(0) (the
+  // sums of a row's four lanes are added at the end, so one lane holds it)
+  float mrow[2] = {opt.sink ? 0.0f : -INFINITY, opt.sink ? 0.0f : -INFINITY};
+  float lrow[2] = {opt.sink && t4 == 0 ? 1.0f : 0.0f, opt.sink && t4 == 0 ? 1.0f : 0.0f};
+  // capped scores are formed from the scaled ones before the softmax; their exponents need no further scale
+  const float sl2 = opt.softcap > 0.0f ? LOG2E : scale * LOG2E;
+  const float cap_in = opt.softcap > 0.0f ? scale / opt.softcap : 0.0f;
 
   const int kend = pos0 + rows;                                  // keys [.., kend) may be seen
   const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0; // first key the first row may see
   const int t_begin = kfirst / BK, t_end = (kend - 1) / BK;
+  // kept first tokens: their tiles come first when the window has passed them (tiles [0, n_keep), then
+  // [t_begin, t_end]); otherwise the window's tiles hold them anyway
+  const int keep = window > 0 ? opt.keep_first : 0;
+  const int n_keep = min((keep + BK - 1) / BK, t_begin);
+  const int n_iter = n_keep + t_end - t_begin + 1;
   __shared__ int bt_s[BT_CACHE];                                 // this block's slice of the block table
   int bt_first = 0;
   {
-    const int b0 = kfirst >> kv.page_shift, b1 = (kend - 1) >> kv.page_shift;
+    const int b0 = keep > 0 ? 0 : kfirst >> kv.page_shift, b1 = (kend - 1) >> kv.page_shift;
     if (b1 - b0 < BT_CACHE) {
       for (int i = tid; i <= b1 - b0; i += 128) bt_s[i] = bt[b0 + i];
       bt = bt_s;
@@ -220,13 +249,16 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
 #pragma unroll
     for (int dp = 0; dp < DT / 2; ++dp) voff[dp] = (unsigned)((((j & 1) * 8 + r) * HD + (((dp * 2 + (j >> 1)) ^ r) << 3)) * 2);
   }
-  load_kv_tile64<HD>(ks, vs, kbase, vbase, kv, bt, t_begin * BK, kfirst, kend, tid, bt_first);
+  const int klo = keep > 0 ? 0 : kfirst;                         // with kept tokens every row is loaded; the mask decides
+  load_kv_tile64<HD>(ks, vs, kbase, vbase, kv, bt, (n_keep ? 0 : t_begin) * BK, klo, kend, tid, bt_first);
   cp_async_commit();
-  for (int t = t_begin; t <= t_end; ++t) {
-    const int st = (t - t_begin) & 1;
-    if (t < t_end) {
-      load_kv_tile64<HD>(ks + (st ^ 1) * BK * HD, vs + (st ^ 1) * BK * HD, kbase, vbase, kv, bt, (t + 1) * BK,
-                         kfirst, kend, tid, bt_first);
+  for (int it = 0; it < n_iter; ++it) {
+    const int t = it < n_keep ? it : t_begin + (it - n_keep);
+    const int st = it & 1;
+    if (it + 1 < n_iter) {
+      const int tn = it + 1 < n_keep ? it + 1 : t_begin + (it + 1 - n_keep);
+      load_kv_tile64<HD>(ks + (st ^ 1) * BK * HD, vs + (st ^ 1) * BK * HD, kbase, vbase, kv, bt, tn * BK,
+                         klo, kend, tid, bt_first);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -235,7 +267,7 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     __syncthreads();
     const int key0 = t * BK;
     const bool active = wr0 < rows && key0 <= warp_last &&
-                        (window <= 0 || key0 + BK > pos0 + wr0 - window + 1);
+                        (window <= 0 || key0 + BK > pos0 + wr0 - window + 1 || key0 < keep);
     if (active) {
       const unsigned kt = ks_addr + (unsigned)(st * BK * HD * 2);
       const unsigned vt = vs_addr + (unsigned)(st * BK * HD * 2);
@@ -254,6 +286,13 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
         }
       }
       // mask (diagonal, window and edge tiles only), row maxima of the raw scores
+      if (opt.softcap > 0.0f) {
+#pragma unroll
+        for (int n = 0; n < BK / 8; ++n) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) s[n][c] = opt.softcap * tanh_exp(s[n][c] * cap_in);
+        }
+      }
       const bool need_mask = key0 + BK - 1 > pos0 + wr0 || window > 0 || key0 < kfirst;
       if (need_mask) {
 #pragma unroll
@@ -262,7 +301,7 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
           for (int c = 0; c < 4; ++c) {
             const int key = key0 + n * 8 + t4 * 2 + (c & 1);
             const int p = (c & 2) ? pb_row : pa_row;
-            const bool vis = key <= p && key < kend && (window <= 0 || key > p - window);
+            const bool vis = key <= p && key < kend && (window <= 0 || key > p - window || key < keep);
             if (!vis) s[n][c] = -INFINITY;
           }
         }
@@ -337,6 +376,20 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   const int ra = wr0 + g, rb = ra + 8;
   bf16* oa = out + (size_t)(tok0 + ra) * out_stride + (size_t)head * HD;
   bf16* ob = out + (size_t)(tok0 + rb) * out_stride + (size_t)head * HD;
+  if (opt.gate) {
+#pragma unroll
+    for (int d = 0; d < DT; ++d) {
+      const int col = head * HD + d * 8 + t4 * 2;
+      float ga[2] = {0.0f, 0.0f}, gb[2] = {0.0f, 0.0f};
+      for (int sl = 0; sl < opt.gate_parts; ++sl) {
+        const float* gp = opt.gate + (size_t)sl * opt.gate_part_stride + col;
+        if (ra < rows) { ga[0] += gp[(size_t)(tok0 + ra) * opt.gate_stride]; ga[1] += gp[(size_t)(tok0 + ra) * opt.gate_stride + 1]; }
+        if (rb < rows) { gb[0] += gp[(size_t)(tok0 + rb) * opt.gate_stride]; gb[1] += gp[(size_t)(tok0 + rb) * opt.gate_stride + 1]; }
+      }
+      o[d][0] *= 1.0f / (1.0f + __expf(-ga[0])); o[d][1] *= 1.0f / (1.0f + __expf(-ga[1]));
+      o[d][2] *= 1.0f / (1.0f + __expf(-gb[0])); o[d][3] *= 1.0f / (1.0f + __expf(-gb[1]));
+    }
+  }
 #pragma unroll
   for (int d = 0; d < DT; ++d) {
     if (ra < rows) *reinterpret_cast<unsigned*>(oa + d * 8 + t4 * 2) = pack_bf16(o[d][0] * inv0, o[d][1] * inv0);
@@ -1051,7 +1104,7 @@ PagedKV make_kv(void* k_layer, void* v_layer, long long page_stride, int page_si
 template <int HD>
 int launch_prefill(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnMeta m,
                    const int* tile_entry, const int* tile_q0, int n_tiles, int n_heads, int n_kv, float scale,
-                   int window, cudaStream_t stream) {
+                   int window, PrefillOptions opt, cudaStream_t stream) {
   const size_t smem = (size_t)4 * 64 * HD * sizeof(bf16);
   auto kern = attn_prefill_bf16_kernel<HD>;
   {  // dynamic plus static shared memory may pass 48 KB
@@ -1059,7 +1112,7 @@ int launch_prefill(const void* q, long long q_stride, void* out, long long out_s
     if (e != cudaSuccess) return (int)e;
   }
   const int ifx_rc = launch_pdl(kern, dim3(n_heads, n_tiles), dim3(128), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m,
-                                                      tile_entry, tile_q0, n_heads, n_kv, scale, window);
+                                                      tile_entry, tile_q0, n_heads, n_kv, scale, window, opt);
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
 }
 
@@ -1132,24 +1185,38 @@ int launch_decode_even(const void* q, long long q_stride, void* out, long long o
 
 // head_dim 64 or 128; page_size a power of two; q rows 4-byte aligned.
 // Query tiles are 64 tokens of one entry (tile_entry / tile_q0).
+IFX_API int ifx_attn_prefill_bf16_ex(const void* q, long long q_stride, void* out, long long out_stride,
+                                  void* k_layer, void* v_layer, long long page_stride, int page_size,
+                                  const int* block_tables, int bt_stride, const int* tile_entry, const int* tile_q0,
+                                  int n_tiles, const int* entry_q_start, const int* entry_q_len,
+                                  const int* entry_ctx_start, int n_heads, int n_kv, int head_dim, float scale,
+                                  int window, float softcap, int keep_first, int sink, const float* gate, int gate_parts,
+                                  long long gate_part_stride, int gate_stride, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (n_kv < 1 || n_heads % n_kv || n_tiles > 65535) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
+  if ((q_stride & 1) || (out_stride & 1) || ((uintptr_t)q & 3) || ((uintptr_t)out & 3)) return IFX_ERR_ALIGNMENT;
+  if ((page_stride & 7) || ((uintptr_t)k_layer & 15) || ((uintptr_t)v_layer & 15)) return IFX_ERR_ALIGNMENT;
+  if (softcap < 0.0f || keep_first < 0) return IFX_ERR_UNSUPPORTED;
+  PrefillOptions opt{softcap, keep_first, sink, gate, gate_parts, gate_part_stride, gate_stride};
+  PagedKV kv = make_kv(k_layer, v_layer, page_stride, page_size, head_dim);
+  AttnMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
+  if (head_dim == 128)
+    return launch_prefill<128>(q, q_stride, out, out_stride, kv, m, tile_entry, tile_q0, n_tiles, n_heads, n_kv, scale, window, opt, stream);
+  if (head_dim == 64)
+    return launch_prefill<64>(q, q_stride, out, out_stride, kv, m, tile_entry, tile_q0, n_tiles, n_heads, n_kv, scale, window, opt, stream);
+  return IFX_ERR_UNSUPPORTED;
+}
+
 IFX_API int ifx_attn_prefill_bf16(const void* q, long long q_stride, void* out, long long out_stride,
                                   void* k_layer, void* v_layer, long long page_stride, int page_size,
                                   const int* block_tables, int bt_stride, const int* tile_entry, const int* tile_q0,
                                   int n_tiles, const int* entry_q_start, const int* entry_q_len,
                                   const int* entry_ctx_start, int n_heads, int n_kv, int head_dim, float scale,
                                   int window, cudaStream_t stream) {
-  if (n_tiles <= 0) return 0;
-  if (n_kv < 1 || n_heads % n_kv || n_tiles > 65535) return IFX_ERR_UNSUPPORTED;
-  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
-  if ((q_stride & 1) || (out_stride & 1) || ((uintptr_t)q & 3) || ((uintptr_t)out & 3)) return IFX_ERR_ALIGNMENT;
-  if ((page_stride & 7) || ((uintptr_t)k_layer & 15) || ((uintptr_t)v_layer & 15)) return IFX_ERR_ALIGNMENT;
-  PagedKV kv = make_kv(k_layer, v_layer, page_stride, page_size, head_dim);
-  AttnMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
-  if (head_dim == 128)
-    return launch_prefill<128>(q, q_stride, out, out_stride, kv, m, tile_entry, tile_q0, n_tiles, n_heads, n_kv, scale, window, stream);
-  if (head_dim == 64)
-    return launch_prefill<64>(q, q_stride, out, out_stride, kv, m, tile_entry, tile_q0, n_tiles, n_heads, n_kv, scale, window, stream);
-  return IFX_ERR_UNSUPPORTED;
+  return ifx_attn_prefill_bf16_ex(q, q_stride, out, out_stride, k_layer, v_layer, page_stride, page_size, block_tables, bt_stride,
+                                  tile_entry, tile_q0, n_tiles, entry_q_start, entry_q_len, entry_ctx_start, n_heads, n_kv,
+                                  head_dim, scale, window, 0.0f, 0, 0, nullptr, 0, 0, 0, stream);
 }
 
 // Scratch: part_o float32 [n_dec * n_heads * n_splits * head_dim], part_ml float32

@@ -147,6 +147,11 @@ def _lib():
                                                   c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                   c_void_p, c_int, c_int, c_int, c_float, c_int,
                                                   c_int, c_float, c_int, c_int, c_void_p, c_int, c_ll, c_int, c_void_p]
+        lib.ifx_attn_prefill_bf16_ex.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
+                                                 c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                 c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_int, c_int,
+                                                 c_void_p, c_int, c_ll, c_int, c_void_p]
+        lib.ifx_attn_prefill_bf16_ex.restype = c_int
         lib.ifx_retention_segment.argtypes = []
         lib.ifx_retention_scan.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float,
                                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -1252,6 +1257,37 @@ def attn_paged_options(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_laye
                                             n_heads, n_kv, head_dim, float(scale), int(window), int(v_dim), float(softcap),
                                             int(keep_first), 1 if sink else 0, gp, g_parts, g_pstride, g_stride, _stream()),
            "attn_paged_options")
+    return out
+
+
+def _gate_slices(gate: Optional[torch.Tensor], width: int, what: str):
+    if gate is None:
+        return None, 0, 0, 0
+    _need(gate.dtype == torch.float32 and gate.stride(-1) == 1 and gate.shape[-1] >= width, f"{what}: gate float32 rows")
+    if gate.dim() == 3:
+        return _ptr(gate), gate.shape[0], gate.stride(0), gate.stride(1)
+    return _ptr(gate), 1, 0, gate.stride(0)
+
+
+def attn_prefill_options_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer: torch.Tensor, v_layer: torch.Tensor,
+                              page_stride: int, page_size: int, block_tables: torch.Tensor, tile_entry: torch.Tensor,
+                              tile_q0: torch.Tensor, n_tiles: int, entry_q_start: torch.Tensor, entry_q_len: torch.Tensor,
+                              entry_ctx_start: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
+                              window: int, softcap: float = 0.0, keep_first: int = 0, sink: bool = False,
+                              gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`attn_prefill_bf16` (tensor cores, bfloat16, keys and values both ``head_dim`` = 64 or 128 wide, query
+    tiles of 64 tokens) with the options of :func:`attn_paged_options`."""
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_layer.dtype == torch.bfloat16,
+          "attn_prefill_options_bf16: bfloat16 operands")
+    _need(head_dim in FAST_ATTENTION_HEAD_DIMS, f"attn_prefill_options_bf16: head_dim {head_dim} not in {FAST_ATTENTION_HEAD_DIMS}")
+    _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "attn: block_tables int32 [R, B]")
+    gp, g_parts, g_pstride, g_stride = _gate_slices(gate, n_heads * head_dim, "attn_prefill_options_bf16")
+    _check(_lib().ifx_attn_prefill_bf16_ex(_ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(k_layer), _ptr(v_layer),
+                                           page_stride, page_size, _ptr(block_tables), block_tables.stride(0),
+                                           _ptr(tile_entry), _ptr(tile_q0), n_tiles, _ptr(entry_q_start),
+                                           _ptr(entry_q_len), _ptr(entry_ctx_start), n_heads, n_kv, head_dim,
+                                           float(scale), int(window), float(softcap), int(keep_first), 1 if sink else 0,
+                                           gp, g_parts, g_pstride, g_stride, _stream()), "attn_prefill_options_bf16")
     return out
 
 

@@ -1,6 +1,6 @@
 """``Pemorax`` as a spec: the one file that knows this architecture.
 
-A plain token embedding; every layer a ``sandwich`` block (an RMS norm ahead of and behind each sublayer) whose
+A plain token embedding; every layer a ``pre_post_norm`` block (an RMS norm ahead of and behind each sublayer) whose
 mixer is ``side_by_side``: ``window_attention`` (short convolution, interleaved rotary positions that may be
 frequency-scaled, capped scores, a window that keeps the first tokens, a sink, a sigmoid gate) beside
 ``retention`` (rotate-half positions, a decay per head, unit norm per head, silu gate), their outputs normed and
@@ -56,7 +56,7 @@ def build_pemorax_spec(cfg: PemoraxConfig) -> ModelSpec:
             else:
                 parts["feed_forward"] = PartSpec("routed_experts", dict(name="mlp", hidden=h, intermediate=layer.mlp["ff"],
                                                                         experts=layer.mlp["experts"], top=layer.mlp["top"]))
-        layers.append(LayerSpec(prefix=f"l{i}", arrangement="sandwich", parts=parts, position=None))
+        layers.append(LayerSpec(prefix=f"l{i}", arrangement="pre_post_norm", parts=parts, position=None))
     return ModelSpec(
         architecture=PemoraxConfig.ARCHITECTURE, hidden_size=h, vocab_size=cfg.vocab, max_position=MAX_POSITION,
         embedding=PartSpec("token_embedding", dict(vocab=cfg.vocab, hidden=h, weight_name="embed")),

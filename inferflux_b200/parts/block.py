@@ -157,7 +157,7 @@ class JunctionBlock:
         return None
 
 
-class SandwichBlock:
+class PrePostNormBlock:
     """A norm ahead of and a norm behind every sublayer:
 
         residual += norm_1b(mixer(norm_1(residual)))
@@ -178,7 +178,7 @@ class SandwichBlock:
         self.ff_norm, self.ff, self.ff_post = (parts.get(r) for r in ("feed_forward_norm", "feed_forward",
                                                                       "feed_forward_post_norm"))
         if (self.ff is None) != (self.ff_norm is None) or (self.ff is None) != (self.ff_post is None):
-            raise ValueError("a sandwich block has a feed-forward with both of its norms or none of the three")
+            raise ValueError("a pre_post_norm block has a feed-forward with both of its norms or none of the three")
         self.position_name = position_name
 
     def forward(self, residual: torch.Tensor, delta, ctx, run: RunInfo):
@@ -191,6 +191,6 @@ class SandwichBlock:
         return NormedDelta(self.ff.forward(x2, ctx), self.ff_post.weight, self.ff_post.eps)
 
 
-register_part("arrangement", "sandwich", SandwichBlock)
+register_part("arrangement", "pre_post_norm", PrePostNormBlock)
 register_part("arrangement", "parallel", ParallelBlock)
 register_part("arrangement", "junction", JunctionBlock)

@@ -32,26 +32,43 @@ from ..weights.loader import MATRIX, VECTOR, WeightSpec
 from .base import KVNeed, Part, RunInfo, StateNeed
 from .linear import Linear
 
-QUERY_TILE = 16     # tokens per query tile of the attention kernel
+QUERY_TILE = 16     # tokens per query tile of the plain attention kernel
+CHUNK_TILE = 64     # tokens per query tile of the tensor-core kernel for prompt portions
+CHUNK_MIN = 8       # an entry with at least this many new tokens goes to the tensor-core kernel (where it serves)
 
 
 @dataclass
 class QueryTiles:
-    """The step's query tiles of QUERY_TILE tokens and the entry of every row: int32 device tensors."""
+    """The step's query tiles and the entry of every row: int32 device tensors.  ``tile_*``: tiles of QUERY_TILE
+    tokens over all entries; ``short_*``: the same over the entries with fewer than CHUNK_MIN new tokens (single
+    decoded tokens among them); ``chunk_*``: tiles of CHUNK_TILE tokens over the other entries."""
 
     tile_entry: torch.Tensor
     tile_q0: torch.Tensor
     n_tiles: int
+    short_entry: torch.Tensor
+    short_q0: torch.Tensor
+    n_short: int
+    chunk_entry: torch.Tensor
+    chunk_q0: torch.Tensor
+    n_chunk: int
     row_entry: torch.Tensor
 
 
 def describe_query_tiles(layout, put) -> QueryTiles:
-    tile_entry, tile_q0 = [], []
+    tile_entry, tile_q0, short_entry, short_q0, chunk_entry, chunk_q0 = [], [], [], [], [], []
     for i in range(layout.n_entries):
-        for q0 in range(0, int(layout.q_len[i]), QUERY_TILE):
+        n = int(layout.q_len[i])
+        for q0 in range(0, n, QUERY_TILE):
             tile_entry.append(i), tile_q0.append(q0)
+            if n < CHUNK_MIN:
+                short_entry.append(i), short_q0.append(q0)
+        if n >= CHUNK_MIN:
+            for q0 in range(0, n, CHUNK_TILE):
+                chunk_entry.append(i), chunk_q0.append(q0)
     rows = np.repeat(np.arange(layout.n_entries), layout.q_len[:layout.n_entries])
-    return QueryTiles(put(tile_entry), put(tile_q0), len(tile_entry), put(rows))
+    return QueryTiles(put(tile_entry), put(tile_q0), len(tile_entry), put(short_entry), put(short_q0), len(short_entry),
+                      put(chunk_entry), put(chunk_q0), len(chunk_entry), put(rows))
 
 
 class WindowAttention(Part):
@@ -64,6 +81,8 @@ class WindowAttention(Part):
 
     family = "mixer"
     describe_key = "query_tiles"
+    #: Switch for tests and measurements: prompt portions of a bfloat16 engine on the tensor-core kernel.
+    TENSOR_CORES = True
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
@@ -162,10 +181,21 @@ class WindowAttention(Part):
         if out is None:
             out = torch.empty((n, self.heads * self.vdim), dtype=x.dtype, device=x.device)
         gate = proj[:, self._channels(self.params):] if self.gate else None
-        ops.attn_paged_options(q, q.stride(0), out, k_layer, v_layer, page_stride, ctx.page_size, ctx.block_tables[g],
-                               step.tile_entry, step.tile_q0, step.n_tiles, ctx.entry_q_start, ctx.entry_q_len,
-                               ctx.entry_ctx_start, self.heads, self.kv_heads, self.dim, self.scale, self.window,
-                               self.vdim, self.softcap, self.keep_first, self.sink, gate)
+        common = (ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start, self.heads, self.kv_heads, self.dim, self.scale,
+                  self.window)
+        fast = (self.TENSOR_CORES and x.dtype == torch.bfloat16 and self.dim == self.vdim and out.is_contiguous()
+                and self.dim in ops.FAST_ATTENTION_HEAD_DIMS and step.n_chunk > 0)
+        if fast:
+            # prompt portions on tensor cores; the step's short entries (single tokens) stay with the plain kernel
+            ops.attn_prefill_options_bf16(q, q.stride(0), out, k_layer, v_layer, page_stride, ctx.page_size,
+                                          ctx.block_tables[g], step.chunk_entry, step.chunk_q0, step.n_chunk, *common,
+                                          self.softcap, self.keep_first, self.sink, gate)
+            tiles = (step.short_entry, step.short_q0, step.n_short)
+        else:
+            tiles = (step.tile_entry, step.tile_q0, step.n_tiles)
+        if tiles[2]:
+            ops.attn_paged_options(q, q.stride(0), out, k_layer, v_layer, page_stride, ctx.page_size, ctx.block_tables[g],
+                                   *tiles, *common, self.vdim, self.softcap, self.keep_first, self.sink, gate)
         return out
 
     def forward(self, x: torch.Tensor, ctx, run: RunInfo, position):

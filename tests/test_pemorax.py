@@ -95,7 +95,7 @@ def test_config_is_read_from_its_own_keys():
     spec = build_spec(cfg)
     # four distinct sets of rotary parameters (the third layer rotates nothing): four tables
     assert sorted(spec.positions) == ["rot0", "rot1", "rot2", "rot3"]
-    assert [l.arrangement for l in spec.layers] == ["sandwich"] * 3 and "feed_forward" not in spec.layers[2].parts
+    assert [l.arrangement for l in spec.layers] == ["pre_post_norm"] * 3 and "feed_forward" not in spec.layers[2].parts
     assert spec.layers[1].parts["feed_forward"].kind == "routed_experts"
     branches = spec.layers[0].parts["mixer"].params["branches"]
     assert [b["kind"] for b in branches] == ["window_attention", "retention"] and branches[0]["position"] == "rot0"
@@ -260,7 +260,8 @@ def test_rotation_alone(layout):
 
 @gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_attention_edges_with_one_score_that_stands_out(dtype):
+@pytest.mark.parametrize("dim,vdim,width", [(16, 12, 64), (64, 64, 128)])     # (64, 64): bfloat16 portions on tensor cores
+def test_attention_edges_with_one_score_that_stands_out(dtype, dim, vdim, width):
     """210 tokens, a window of 40 that keeps the first 5, pages of 16.  Head 0's query is the token's first 16
     numbers and its key the next 16, nothing rotates and nothing is convolved; each of the last eight tokens gets
     a query that matches the key of one chosen earlier token and no other: the last one inside its window, the
@@ -268,15 +269,16 @@ def test_attention_edges_with_one_score_that_stands_out(dtype):
     the very first token, and itself.  A visible target takes the whole weight, an invisible one leaves the sink
     with it; a window, a kept count or a page's edge that is off by one changes the result entirely.  The first
     two of the eight queries come inside a portion, the others as single tokens."""
-    n, dim, wn, keep = 210, 16, 40, 5
-    left = dict(heads=2, kv_heads=1, dim=dim, vdim=12, mask=dict(size=wn, keep_first=keep), scale=1.0)
-    cfg = dict(PX["A"], layers=[dict(type="parallel", mixer=dict(left=left, right=PX["A"]["layers"][2]["mixer"]["right"]), mlp=None)])
+    n, wn, keep = 210, 40, 5
+    left = dict(heads=2, kv_heads=1, dim=dim, vdim=vdim, mask=dict(size=wn, keep_first=keep), scale=1.0)
+    cfg = dict(PX["A"], width=width,
+               layers=[dict(type="parallel", mixer=dict(left=left, right=PX["A"]["layers"][2]["mixer"]["right"]), mlp=None)])
     _, tensors = pemorax_tensors(cfg, 21)
     eye = torch.eye(dim)
-    tensors["l0.mix.left.q"] = torch.cat([torch.cat([eye, torch.zeros(dim, 48)], 1), _rand((dim, 64), 22, 0.05)]).to(torch.bfloat16)
-    tensors["l0.mix.left.k"] = torch.cat([torch.zeros(dim, dim), eye, torch.zeros(dim, 32)], 1).to(torch.bfloat16)
+    tensors["l0.mix.left.q"] = torch.cat([torch.cat([eye, torch.zeros(dim, width - dim)], 1), _rand((dim, width), 22, 0.05)]).to(torch.bfloat16)
+    tensors["l0.mix.left.k"] = torch.cat([torch.zeros(dim, dim), eye, torch.zeros(dim, width - 2 * dim)], 1).to(torch.bfloat16)
     model, runner, w = _runner_for(cfg, dtype, 21, tensors=tensors)
-    x = _rand((n, 64), 23, 0.3).to(torch.bfloat16).float()
+    x = _rand((n, width), 23, 0.3).to(torch.bfloat16).float()
     x[:, :2 * dim] *= 0.1                                        # quiet queries and keys, but for the chosen pairs
     first_q = n - 8
     targets = [p - off if off is not None else t for p, (off, t) in zip(range(first_q, n), [
