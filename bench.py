@@ -184,22 +184,43 @@ def kunonex_config(size: str, layers: int):
                 layers=[gru if i % 3 == 0 else attn for i in range(layers)], loop=None)
 
 
+def pemorax_config(size: str, layers: int):
+    """A Pemorax config.json at the widths of one of the family sizes above: every layer attention (the family's
+    heads and kv heads of 128, a window of 1,024 that keeps 4, four taps, scaled interleaved rotary positions,
+    capped scores) beside retention (half as many heads of 128 x 128), feed-forwards in turn dense (the family's
+    width) and 16 experts of a quarter of that width of which a token takes 4 (as many active weights)."""
+    _, hidden, heads, kv_heads, inter, vocab, _ = SIZES[size]
+    left = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, conv=4, mask=dict(size=1024, keep_first=4),
+                rot=dict(dims=128, base=1000000.0, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)),
+                scale=128 ** -0.5, softcap=50.0)
+    rheads = max(1, heads // 2)
+    right = dict(heads=rheads, dim=128, vdim=128, decay=[1.0 - 2.0 ** (-5 - 3 * i / rheads) for i in range(rheads)],
+                 rot=dict(dims=128, base=10000.0))
+    dense = dict(kind="dense", ff=inter)
+    moe = dict(kind="moe", expert=dict(ff=inter // 4 // 8 * 8), router=dict(experts=16, top=4))
+    return dict(architecture="Pemorax", width=hidden, vocab=vocab, norm=dict(eps=1e-6),
+                layers=[dict(type="parallel", mixer=dict(left=left, right=right), mlp=moe if i % 2 else dense)
+                        for i in range(layers)])
+
+
 def architecture_workload(args) -> int:
-    """--arch kunonex: prefill (one 2,048-token prompt) and decode (batch 8 at the given context) of a Kunonex
-    model beside a Qwen2 model of the same width, layer count, feed-forward width and vocabulary, both with
-    random bfloat16 weights, device-timed with CUDA events after warm-up.  One JSON line."""
+    """--arch kunonex / pemorax: prefill (one 2,048-token prompt) and decode (batch 8 at the given context) of a
+    model of that design beside a Qwen2 model of the same width, layer count, feed-forward width and vocabulary,
+    both with random bfloat16 weights, device-timed with CUDA events after warm-up.  One JSON line."""
     import torch
     from inferflux_b200 import Engine, SamplingParams, StepEntry
     layers = args.layers or 8
     ctx, batch, T = args.context, args.batch, 2048
     warmup = max(3, args.warmup)
     greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
-    out = {"metric": f"prefill and decode tokens/s, Kunonex beside Qwen2 at the {args.size.upper()} widths", "impl": "ours",
+    arch = args.arch
+    design = {"kunonex": kunonex_config, "pemorax": pemorax_config}[arch]
+    out = {"metric": f"prefill and decode tokens/s, {arch.capitalize()} beside Qwen2 at the {args.size.upper()} widths", "impl": "ours",
            "n_gpus": 1, "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random token ids",
            "steps": args.steps, "warmup": warmup,
            "config": {"layers": layers, "size": args.size, "global_batch": batch, "seq_len": ctx, "prefill_tokens": T,
                       "l2": "weights and cache exceed L2; no flush"}}
-    for name, cfgd in (("kunonex", kunonex_config(args.size, layers)),
+    for name, cfgd in ((arch, design(args.size, layers)),
                        ("qwen2", dict(family_config(args.size), num_hidden_layers=layers))):
         vocab = cfgd.get("vocab") or cfgd["vocab_size"]
         eng = Engine.from_config(cfgd, seed=0, dtype="bfloat16", kv_cache_tokens=batch * (ctx + 64) + T, max_seqs=batch + 1,
@@ -245,7 +266,7 @@ def architecture_workload(args) -> int:
                      "weight_bytes": eng.model.weight_bytes, "clocks": clocks}
         del eng, runner
         torch.cuda.empty_cache()
-    out["value"] = out["kunonex"]["decode_tokens_per_s"]
+    out["value"] = out[arch]["decode_tokens_per_s"]
     out["unit"] = "tokens/s"
     print(json.dumps(out))
     return 0
@@ -267,12 +288,12 @@ def main() -> int:
     ap.add_argument("--mixed", type=int, default=0, metavar="N",
                     help="instead of the decode step: N requests with prompts of 128 to 2,048 tokens and 256 output "
                          "tokens each through Engine.generate (chunked prompts beside decoding requests)")
-    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "kunonex"],
-                    help="kunonex: instead of the default workload, a Kunonex model beside a Qwen2 model of equal size "
-                         "(--size, --layers, default 8), prefill and decode")
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "kunonex", "pemorax"],
+                    help="kunonex or pemorax: instead of the default workload, a model of that design beside a Qwen2 model "
+                         "of equal size (--size, --layers, default 8), prefill and decode")
     args = ap.parse_args()
 
-    if args.arch == "kunonex" and args.impl == "ours":
+    if args.arch in ("kunonex", "pemorax") and args.impl == "ours":
         return architecture_workload(args)
     if args.impl == "reference":
         return reference_arm()

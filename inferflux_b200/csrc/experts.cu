@@ -195,6 +195,44 @@ int launch_products(const void* x, const void* w_gate_up, const void* w_down, co
 }
 }  // namespace
 
+// xs[r] = x[pair / top] for the pair at sorted row r, zeros where a row holds no pair
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ sorted_pair, T* __restrict__ xs, int hidden, int top) {
+  pdl_enter();
+  const int r = blockIdx.x;
+  const int pair = sorted_pair[r];
+  const T* src = pair >= 0 ? x + (size_t)(pair / top) * hidden : nullptr;
+  T* dst = xs + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = src ? src[i] : Num<T>::from_f(0.0f);
+}
+
+// The sort alone (for callers that run the tiles' products with a kernel of their own): tile = rows per tile.
+IFX_API int ifx_moe_group(const int* chosen, int pairs, int experts, int tile, int max_tiles, int* tile_expert,
+                          int* sorted_pair, int* pair_row, cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  if (tile < 1 || max_tiles < pairs / tile + experts || experts > 4096) return IFX_ERR_UNSUPPORTED;
+  const int rc = launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)3 * experts * sizeof(int), stream, chosen, pairs,
+                            experts, tile, max_tiles, tile_expert, sorted_pair, pair_row);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
+IFX_API int ifx_moe_gather_rows(const void* x, int dtype, const int* sorted_pair, void* xs, int rows, int hidden, int top,
+                                cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int rc = dtype == IFX_BF16
+      ? launch_pdl(moe_gather_rows_kernel<bf16>, dim3(rows), dim3(256), 0, stream, (const bf16*)x, sorted_pair, (bf16*)xs, hidden, top)
+      : launch_pdl(moe_gather_rows_kernel<float>, dim3(rows), dim3(256), 0, stream, (const float*)x, sorted_pair, (float*)xs, hidden, top);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
+IFX_API int ifx_moe_combine(const float* y, const int* pair_row, const float* weights, float* out, int n_tokens, int hidden,
+                            int top, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  const int rc = launch_pdl(moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, y, pair_row, weights, out, hidden, top);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
 IFX_API int ifx_moe_route(const float* logits, int n_tokens, int experts, int top, int* chosen, float* weights,
                           cudaStream_t stream) {
   if (n_tokens <= 0) return 0;

@@ -174,7 +174,11 @@ template <int MODE, typename TOut>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       TOut* __restrict__ out, long long ldo, const float* __restrict__ bias, int M, int n_out, int K,
-                      int tile_n, int* __restrict__ error_flag, int k_parts, long long part_stride, QkvEpilogue qe) {
+                      int tile_n, int* __restrict__ error_flag, int k_parts, long long part_stride, QkvEpilogue qe,
+                      const int* __restrict__ tile_expert, int expert_rows) {
+  // tile_expert (modes 0 and 1, or null): the rows of A are sorted by expert into groups of 256, tile_expert[i]
+  // names the expert whose weights row tile i multiplies (its rows of W start at expert * expert_rows) or is
+  // negative for a row tile that is not in use, which every role of the kernel skips.
   constexpr bool SWIGLU = MODE == 1, SKINNY = MODE == 2, QKV = MODE == 3;
   pdl_enter();
   extern __shared__ unsigned char g_smem_raw[];
@@ -226,9 +230,15 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       int stage = 0;
       unsigned phase = 0;
       for (int t = pair; t < tiles && !gave_up; t += n_pairs) {
+        int w_first = 0;
+        if (tile_expert) {
+          const int e = tile_expert[t % m_tiles];
+          if (e < 0) continue;
+          w_first = e * expert_rows;
+        }
         const int m0 = (t % m_tiles) * 256 + (int)rank * 128;
         const int n0 = SKINNY ? 0 : (t / m_tiles) * out_cols;
-        const int w_row = SWIGLU ? (int)rank * n_out + n0 : n0 + (int)rank * w_half_rows;
+        const int w_row = w_first + (SWIGLU ? (int)rank * n_out + n0 : n0 + (int)rank * w_half_rows);
         const int ks0 = SKINNY ? (t / m_tiles) * part_steps : 0, ks1 = SKINNY ? min(k_steps, ks0 + part_steps) : k_steps;
         for (int ks = ks0; ks < ks1; ++ks) {
           if (!g_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) { gave_up = true; break; }
@@ -246,9 +256,11 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       int stage = 0, count = 0;
       unsigned phase = 0;
       const unsigned idesc = P_IDESC | ((unsigned)(tile_n >> 3) << 17);
-      for (int t = pair; t < tiles && !gave_up; t += n_pairs, ++count) {
+      for (int t = pair; t < tiles && !gave_up; t += n_pairs) {
+        if (tile_expert && tile_expert[t % m_tiles] < 0) continue;
         const int acc = count & 1;
         const unsigned acc_parity = (unsigned)(count >> 1) & 1u;
+        ++count;
         if (!g_wait(bar_acc_empty + 8 * acc, acc_parity ^ 1u, abort_flag)) { gave_up = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const unsigned d = tmem + (unsigned)(acc * 256);
@@ -270,9 +282,11 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int row_in_tile = (int)rank * 128 + quarter * 32 + lane;
     const bool vec = (ldo % 8 == 0) && ((uintptr_t)out % 16 == 0);
     int count = 0;
-    for (int t = pair; t < tiles; t += n_pairs, ++count) {
+    for (int t = pair; t < tiles; t += n_pairs) {
+      if (tile_expert && tile_expert[t % m_tiles] < 0) continue;
       const int acc = count & 1;
       const unsigned acc_parity = (unsigned)(count >> 1) & 1u;
+      ++count;
       const int m0 = (t % m_tiles) * 256, n0 = SKINNY ? 0 : (t / m_tiles) * out_cols;
       if (!g_wait(bar_acc_full + 8 * acc, acc_parity, abort_flag)) { gave_up = true; break; }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -471,7 +485,35 @@ int launch_gemm_pair(const void* A, long long lda, const void* W, const float* b
   const int tiles = ((M + 255) / 256) * ((n_out + out_cols - 1) / out_cols);
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   rc = launch_pdl_cluster(kern, dim3(2 * pairs), dim3(P_THREADS), (size_t)P_SMEM, stream, dim3(2, 1, 1), map_a, map_w, (TOut*)out,
-                          ldo, bias, M, n_out, K, tile_n, error_flag, 1, 0ll, QkvEpilogue{});
+                          ldo, bias, M, n_out, K, tile_n, error_flag, 1, 0ll, QkvEpilogue{}, (const int*)nullptr, 0);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
+// The same product over rows sorted by expert into groups of 256: row tile i of A multiplies the weights of
+// expert tile_expert[i] (W is [experts][n_out or 2 n_out][K] as one matrix) or is skipped when that is negative.
+template <bool SWIGLU, typename TOut>
+int launch_gemm_grouped(const void* A, long long lda, const void* W, void* out, long long ldo, int M, int n_out, int K,
+                        int experts, const int* tile_expert, int* error_flag, cudaStream_t stream) {
+  auto kern = gemm_umma_pair_kernel<SWIGLU ? 1 : 0, TOut>;
+  static int sms = 0;
+  if (!sms) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    int dev = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+  }
+  const int tile_n = SWIGLU ? 256 : pick_tile_n(M, n_out, sms / 2);
+  const int out_cols = SWIGLU ? 128 : tile_n;
+  const int expert_rows = SWIGLU ? 2 * n_out : n_out;
+  CUtensorMap map_a, map_w;
+  int rc = make_map(&map_a, A, M, K, lda, 128);
+  if (!rc) rc = make_map(&map_w, W, (long long)experts * expert_rows, K, K, tile_n / 2);
+  if (rc) return rc;
+  const int tiles = ((M + 255) / 256) * ((n_out + out_cols - 1) / out_cols);
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  rc = launch_pdl_cluster(kern, dim3(2 * pairs), dim3(P_THREADS), (size_t)P_SMEM, stream, dim3(2, 1, 1), map_a, map_w, (TOut*)out,
+                          ldo, (const float*)nullptr, M, n_out, K, tile_n, error_flag, 1, 0ll, QkvEpilogue{}, tile_expert, expert_rows);
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 
@@ -518,7 +560,7 @@ int launch_gemm_qkv(const void* A, long long lda, const void* W, const float* bi
   const int tiles = ((M + 255) / 256) * ((n_out + tile_n - 1) / tile_n);
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   rc = launch_pdl_cluster(kern, dim3(2 * pairs), dim3(P_THREADS), (size_t)P_SMEM, stream, dim3(2, 1, 1), map_a, map_w, q_out,
-                          ldo, bias, M, n_out, K, tile_n, error_flag, 1, 0ll, qe);
+                          ldo, bias, M, n_out, K, tile_n, error_flag, 1, 0ll, qe, (const int*)nullptr, 0);
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 
@@ -542,7 +584,7 @@ int launch_gemm_skinny(const void* X, long long ldx, const void* W, float* out, 
   const int tiles = ((n_out + 255) / 256) * k_parts;
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   rc = launch_pdl_cluster(kern, dim3(2 * pairs), dim3(P_THREADS), (size_t)P_SMEM, stream, dim3(2, 1, 1), map_w, map_x, out, ldo,
-                          (const float*)nullptr, n_out, tokens, K, tile_n, error_flag, k_parts, part_stride, QkvEpilogue{});
+                          (const float*)nullptr, n_out, tokens, K, tile_n, error_flag, k_parts, part_stride, QkvEpilogue{}, (const int*)nullptr, 0);
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 }  // namespace
@@ -580,6 +622,26 @@ IFX_API int ifx_gemm_umma_skinny(const void* X, long long ldx, const void* W, fl
   if ((k_steps + per - 1) / per != k_parts) return IFX_ERR_UNSUPPORTED;            // a part would be empty
   if (((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)out & 3)) return IFX_ERR_ALIGNMENT;
   return launch_gemm_skinny(X, ldx, W, out, ldo, tokens, n_out, K, k_parts, part_stride, error_flag, stream);
+}
+
+// Rows of A sorted by expert in groups of 256 (M a multiple of 256): out[row] = A[row] W_e^T with e =
+// tile_expert[row / 256], rows of unused groups (negative) untouched.  swiglu: W_e = [gate rows; up rows],
+// out = silu(gate) * up in bfloat16; otherwise out float32 or bfloat16 by out_dtype.
+IFX_API int ifx_gemm_umma_grouped(const void* A, long long lda, const void* W, void* out, long long ldo, int out_dtype,
+                                  int M, int n_out, int K, int swiglu, int experts, const int* tile_expert,
+                                  int* error_flag, cudaStream_t stream) {
+  if (M <= 0 || n_out <= 0) return 0;
+  if (K <= 0 || (K % 8) || (lda % 8) || (M % 256) || experts < 1 || !tile_expert) return IFX_ERR_UNSUPPORTED;
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return IFX_ERR_ALIGNMENT;
+  if (swiglu) {
+    if (out_dtype != IFX_BF16) return IFX_ERR_UNSUPPORTED;
+    return launch_gemm_grouped<true, bf16>(A, lda, W, out, ldo, M, n_out, K, experts, tile_expert, error_flag, stream);
+  }
+  if (out_dtype == IFX_BF16)
+    return launch_gemm_grouped<false, bf16>(A, lda, W, out, ldo, M, n_out, K, experts, tile_expert, error_flag, stream);
+  if (out_dtype == IFX_F32)
+    return launch_gemm_grouped<false, float>(A, lda, W, out, ldo, M, n_out, K, experts, tile_expert, error_flag, stream);
+  return IFX_ERR_UNSUPPORTED;
 }
 
 IFX_API int ifx_gemm_umma_skinny_parts(int n_out, int K) {

@@ -164,6 +164,13 @@ def _lib():
         lib.ifx_moe_experts.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_void_p]
+        lib.ifx_moe_group.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+        lib.ifx_moe_gather_rows.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_gemm_umma_grouped.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int,
+                                              c_void_p, c_void_p, c_void_p]
+        for name in ("ifx_moe_group", "ifx_moe_gather_rows", "ifx_moe_combine", "ifx_gemm_umma_grouped"):
+            getattr(lib, name).restype = c_int
         for name in ("ifx_norm_chain", "ifx_conv_rope_kv_write", "ifx_rotate_heads", "ifx_attn_paged_generic_ex",
                      "ifx_retention_segment", "ifx_retention_scan", "ifx_retention_finish", "ifx_gelu_tanh",
                      "ifx_moe_route", "ifx_moe_tile_rows", "ifx_moe_experts"):
@@ -1356,6 +1363,37 @@ def moe_route(logits: torch.Tensor, top: int):
     return chosen, weights
 
 
+#: bfloat16 steps with at least this many (token, expert) pairs run the experts' products on the tcgen05 kernel
+#: (row tiles of 256 of one expert each); fewer pairs, float32 and sizes that are no multiple of 8 take the FFMA tiles.
+MOE_TENSOR_CORES = True
+MOE_TENSOR_CORE_PAIRS = 512
+MOE_UMMA_TILE = 256
+
+
+def _moe_experts_umma(x, w_gate_up, w_down, chosen, weights, n, hidden, ff, experts, top) -> torch.Tensor:
+    lib, dev, tile = _lib(), x.device, MOE_UMMA_TILE
+    pairs = n * top
+    max_tiles = pairs // tile + experts
+    rows = max_tiles * tile
+    tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    sorted_pair = torch.empty(rows, dtype=torch.int32, device=dev)
+    pair_row = torch.empty(pairs, dtype=torch.int32, device=dev)
+    _check(lib.ifx_moe_group(_ptr(chosen), pairs, experts, tile, max_tiles, _ptr(tile_expert), _ptr(sorted_pair),
+                             _ptr(pair_row), _stream()), "moe_group")
+    xs = torch.empty((rows, hidden), dtype=x.dtype, device=dev)
+    _check(lib.ifx_moe_gather_rows(_ptr(x), _code(x), _ptr(sorted_pair), _ptr(xs), rows, hidden, top, _stream()), "moe_gather_rows")
+    act = torch.empty((rows, ff), dtype=x.dtype, device=dev)
+    flag = error_flag(dev)
+    _check(lib.ifx_gemm_umma_grouped(_ptr(xs), hidden, _ptr(w_gate_up), _ptr(act), ff, BF16, rows, ff, hidden, 1, experts,
+                                     _ptr(tile_expert), _ptr(flag), _stream()), "gemm_umma_grouped (gate, up)")
+    y = torch.empty((rows, hidden), dtype=torch.float32, device=dev)
+    _check(lib.ifx_gemm_umma_grouped(_ptr(act), ff, _ptr(w_down), _ptr(y), hidden, F32, rows, hidden, ff, 0, experts,
+                                     _ptr(tile_expert), _ptr(flag), _stream()), "gemm_umma_grouped (down)")
+    out = torch.empty((n, hidden), dtype=torch.float32, device=dev)
+    _check(lib.ifx_moe_combine(_ptr(y), _ptr(pair_row), _ptr(weights), _ptr(out), n, hidden, top, _stream()), "moe_combine")
+    return out
+
+
 def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor,
                 weights: torch.Tensor) -> torch.Tensor:
     """``out[t] = sum_k weights[t, k] * W_down[e] (silu(W_gate[e] x_t) * (W_up[e] x_t))``, ``e = chosen[t, k]``:
@@ -1368,6 +1406,8 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
           "moe_experts: contiguous operands of one type")
     _need(tuple(w_down.shape) == (experts, hidden, ff) and w_gate_up.shape[2] == hidden, "moe_experts: weight shapes")
     pairs = n * top
+    if (MOE_TENSOR_CORES and x.dtype == torch.bfloat16 and pairs >= MOE_TENSOR_CORE_PAIRS and hidden % 8 == 0 and ff % 8 == 0):
+        return _moe_experts_umma(x, w_gate_up, w_down, chosen, weights, n, hidden, ff, experts, top)
     tile = int(_lib().ifx_moe_tile_rows(pairs))
     max_tiles = pairs // tile + experts
     dev = x.device
