@@ -11,6 +11,7 @@
 // of 32 keys, and serves prompt portions (any number of cached tokens before
 // them) and single decoded tokens alike.  A window w > 0 hides keys j <= p - w.
 //
+// A second kernel serves steps' single tokens (attn_single_token_kernel below).
 // Options (AttnOptions; all off for plain attention): values of another width than keys (`v_dim`); a cap on
 // the scores, s <- cap * tanh(s / cap); kept first tokens, which stay visible behind the window
 // (key j visible iff j <= p and (p - j < w or j < keep_first)); a sink, one more term of score 0 and no value
@@ -175,6 +176,138 @@ attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __rest
   }
 }
 
+// Single tokens: one block a (token, head), its warps take the key tiles of 32 in turn (a lane a key for the
+// scores, a lane a few value dimensions for the sum), each warp with a running maximum, sum and result of its
+// own that the block merges at the end; keys and values are read straight from the pages.  The same options.
+constexpr int DEC_WARPS = 8;
+
+template <typename T, int NACC>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attn_single_token_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long out_stride,
+                         PagedKV kv, AttnBatch b, int n_heads, int n_kv, int head_dim, float scale, int window,
+                         AttnOptions opt) {
+  pdl_enter();
+  extern __shared__ float smem[];
+  const int v_dim = opt.v_dim;
+  float* qs = smem;                                   // [head_dim]
+  float* wm = qs + head_dim;                          // [DEC_WARPS] maxima
+  float* wl = wm + DEC_WARPS;                         // [DEC_WARPS] sums
+  float* wo = wl + DEC_WARPS;                         // [DEC_WARPS][v_dim]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int e = b.tile_entry[blockIdx.x], head = blockIdx.y;
+  const int tok = b.entry_q_start[e] + b.tile_q0[blockIdx.x];
+  const int p = b.entry_ctx_start[e] + b.tile_q0[blockIdx.x];          // the token's position = its last visible key
+  const int kvh = head / (n_heads / n_kv);
+  const int* bt = b.block_tables + (size_t)e * b.bt_stride;
+  const T* kc = (const T*)kv.k + (size_t)kvh * kv.head_stride;
+  const T* vc = (const T*)kv.v + (size_t)kvh * opt.v_head_stride;
+  for (int d = tid; d < head_dim; d += blockDim.x) qs[d] = Num<T>::to_f(q[(size_t)tok * q_stride + (size_t)head * head_dim + d]);
+  __syncthreads();
+  int kstart = 0;
+  if (window > 0) kstart = max(0, p - window + 1) & ~(BKEYS - 1);
+  const int keep_end = window > 0 ? min((opt.keep_first + BKEYS - 1) & ~(BKEYS - 1), kstart) : 0;
+  const int n_keep = keep_end / BKEYS, n_tiles = n_keep + (p - kstart) / BKEYS + 1;
+  float m = -INFINITY, l = 0.0f, o[NACC];
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) o[a] = 0.0f;
+  for (int it = warp; it < n_tiles; it += DEC_WARPS) {
+    const int k0 = it < n_keep ? it * BKEYS : kstart + (it - n_keep) * BKEYS;
+    const int key = k0 + lane;
+    const bool visible = key <= p && (window <= 0 || key > p - window || key < opt.keep_first);
+    const int page = key <= p ? bt[key >> kv.page_shift] : -1;
+    float sc = -INFINITY;
+    if (visible && page >= 0) {
+      const T* kr = kc + (size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * head_dim;
+      float dot = 0.0f;
+      if (sizeof(T) == 2 && (head_dim & 7) == 0 && kv.page_size >= 8) {
+        for (int d = 0; d < head_dim; d += 8) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(kr + d);
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float2 f = __bfloat1622float2(h2[u]);
+            dot = fmaf(qs[d + 2 * u], f.x, dot);
+            dot = fmaf(qs[d + 2 * u + 1], f.y, dot);
+          }
+        }
+      } else {
+        for (int d = 0; d < head_dim; ++d) dot = fmaf(qs[d], Num<T>::to_f(kr[d]), dot);
+      }
+      sc = dot * scale;
+      if (opt.softcap > 0.0f) sc = opt.softcap * tanhf(sc / opt.softcap);
+    }
+    const float m_new = fmaxf(m, warp_max(sc));
+    if (m_new == -INFINITY) continue;                 // warp-uniform: nothing visible in this tile
+    const float alpha = expf(m - m_new);
+    const float pj = sc == -INFINITY ? 0.0f : expf(sc - m_new);
+    l = l * alpha + warp_sum(pj);
+    m = m_new;
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) o[a] *= alpha;
+    for (int j = 0; j < BKEYS; ++j) {
+      const float pjj = __shfl_sync(0xffffffffu, pj, j);
+      const int pg = __shfl_sync(0xffffffffu, page, j);
+      if (pjj == 0.0f) continue;                      // warp-uniform; keeps stale values out
+      const T* vr = vc + (size_t)pg * kv.page_stride + (size_t)((k0 + j) & (kv.page_size - 1)) * v_dim;
+#pragma unroll
+      for (int a = 0; a < NACC; ++a) {
+        const int d = lane + 32 * a;
+        if (d < v_dim) o[a] = fmaf(pjj, Num<T>::to_f(vr[d]), o[a]);
+      }
+    }
+  }
+  if (lane == 0) { wm[warp] = m; wl[warp] = l; }
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) {
+    const int d = lane + 32 * a;
+    if (d < v_dim) wo[warp * v_dim + d] = o[a];
+  }
+  __syncthreads();
+  if (warp == 0) {                                    // the merge: warps in index order, the sink as one more term exp(0)
+    float mm = opt.sink ? 0.0f : -INFINITY;
+    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, wm[w]);
+    float ll = opt.sink ? expf(0.0f - mm) : 0.0f;
+    float f[DEC_WARPS];
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      f[w] = wm[w] == -INFINITY ? 0.0f : expf(wm[w] - mm);
+      ll += wl[w] * f[w];
+    }
+    const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;
+    T* orow = out + (size_t)tok * out_stride + (size_t)head * v_dim;
+    for (int d = lane; d < v_dim; d += 32) {
+      float y = 0.0f;
+      for (int w = 0; w < DEC_WARPS; ++w) y = fmaf(wo[w * v_dim + d], f[w], y);
+      y *= inv;
+      if (opt.gate) {
+        float g = 0.0f;
+        for (int sl = 0; sl < opt.gate_parts; ++sl)
+          g += opt.gate[(size_t)sl * opt.gate_part_stride + (size_t)tok * opt.gate_stride + (size_t)head * v_dim + d];
+        y *= 1.0f / (1.0f + expf(-g));
+      }
+      orow[d] = Num<T>::from_f(y);
+    }
+  }
+}
+
+template <typename T, int NACC>
+int launch_single(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnBatch b,
+                  int n_tiles, int n_heads, int n_kv, int head_dim, float scale, int window, AttnOptions opt, cudaStream_t stream) {
+  const size_t smem = ((size_t)head_dim + 2 * DEC_WARPS + (size_t)DEC_WARPS * opt.v_dim) * sizeof(float);
+  const int rc = launch_pdl(attn_single_token_kernel<T, NACC>, dim3(n_tiles, n_heads), dim3(DEC_WARPS * 32), smem, stream,
+                            (const T*)q, q_stride, (T*)out, out_stride, kv, b, n_heads, n_kv, head_dim, scale, window, opt);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
+template <typename T>
+int dispatch_single(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnBatch b,
+                    int n_tiles, int n_heads, int n_kv, int head_dim, float scale, int window, AttnOptions opt, cudaStream_t stream) {
+  const int nacc = (opt.v_dim + 31) / 32;
+  if (nacc <= 1) return launch_single<T, 1>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
+  if (nacc <= 2) return launch_single<T, 2>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
+  if (nacc <= 4) return launch_single<T, 4>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
+  return launch_single<T, 8>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
+}
+
 template <typename T, int NACC>
 int launch_generic(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnBatch b,
                    int n_tiles, int n_heads, int n_kv, int head_dim, float scale, int window, AttnOptions opt, cudaStream_t stream) {
@@ -212,7 +345,7 @@ IFX_API int ifx_attn_paged_generic_ex(const void* q, long long q_stride, void* o
                                       int n_heads, int n_kv, int head_dim, float scale, int window,
                                       int v_dim, float softcap, int keep_first, int sink,
                                       const float* gate, int gate_parts, long long gate_part_stride, int gate_stride,
-                                      cudaStream_t stream) {
+                                      int single_tokens, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (head_dim < 1 || head_dim > 256 || v_dim < 1 || v_dim > 256 || n_kv < 1 || n_heads % n_kv) return IFX_ERR_UNSUPPORTED;
   if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
@@ -223,6 +356,13 @@ IFX_API int ifx_attn_paged_generic_ex(const void* q, long long q_stride, void* o
   while ((1 << kv.page_shift) < page_size) ++kv.page_shift;
   AttnBatch b{block_tables, bt_stride, tile_entry, tile_q0, entry_q_start, entry_q_len, entry_ctx_start};
   AttnOptions opt{v_dim, page_size * v_dim, softcap, keep_first, sink, gate, gate_parts, gate_part_stride, gate_stride};
+  if (single_tokens) {            // every tile is one token (tile_q0 = its place in its entry): the kernel for those
+    if (dtype == IFX_F32)
+      return dispatch_single<float>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
+    if (dtype == IFX_BF16)
+      return dispatch_single<bf16>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
+    return IFX_ERR_UNSUPPORTED;
+  }
   if (dtype == IFX_F32)
     return dispatch_generic<float>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
   if (dtype == IFX_BF16)
@@ -240,5 +380,5 @@ IFX_API int ifx_attn_paged_generic(const void* q, long long q_stride, void* out,
   return ifx_attn_paged_generic_ex(q, q_stride, out, out_stride, dtype, k_layer, v_layer, page_stride, page_size,
                                    block_tables, bt_stride, tile_entry, tile_q0, n_tiles, entry_q_start, entry_q_len,
                                    entry_ctx_start, n_heads, n_kv, head_dim, scale, window, head_dim, 0.0f, 0, 0,
-                                   nullptr, 0, 0, 0, stream);
+                                   nullptr, 0, 0, 0, 0, stream);
 }

@@ -169,6 +169,94 @@ moe_product_kernel(const TA* __restrict__ A, long long lda, int gather_div /* 0:
   }
 }
 
+// The same tile product for bfloat16 and short tiles (16 rows: steps of single tokens) on tensor cores: the 16 rows
+// are the rows of one m16n8k16 MMA, a warp owns 16 of the block's 64 rows of W_e (SwiGLU: 8 gate rows and the 8 up
+// rows that belong to them), operands go through shared memory 64 K at a time by 16-byte loads.  Such a step is
+// bound by reading the chosen experts' weights once; the arithmetic of the FFMA tiles above took three times as long.
+__device__ __forceinline__ void moe_mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TO, bool SWIGLU>
+__global__ void __launch_bounds__(128)
+moe_product_mma_kernel(const bf16* __restrict__ A, long long lda, int gather_div, const bf16* __restrict__ W,
+                       const int* __restrict__ tile_expert, const int* __restrict__ sorted_pair, TO* __restrict__ C,
+                       long long ldc, int n_out, int K) {
+  constexpr int BM = 16, BN = 64, BK = 64, LD = BK + 8;
+  pdl_enter();
+  __shared__ __align__(16) bf16 As[BM][LD];
+  __shared__ __align__(16) bf16 Ws[BN][LD];
+  __shared__ int rows[BM];
+  const int tile = blockIdx.y;
+  const int e = tile_expert[tile];
+  if (e < 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  constexpr int cols = SWIGLU ? BN / 2 : BN;
+  const int n0 = blockIdx.x * cols;
+  const bf16* We = W + (size_t)e * (SWIGLU ? 2 : 1) * n_out * K;
+  if (tid < BM) {
+    const int pair = sorted_pair[tile * BM + tid];
+    rows[tid] = pair < 0 ? -1 : (gather_div ? pair / gather_div : tile * BM + tid);
+  }
+  __syncthreads();
+  // the two rows of W_e's tile that feed this thread's two accumulators, and which output columns they are
+  const int r0 = SWIGLU ? 8 * warp + g : 16 * warp + g;
+  const int r1 = SWIGLU ? cols + 8 * warp + g : 16 * warp + 8 + g;
+  float acc0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, acc1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    {
+      const int r = tid >> 3, c8 = (tid & 7) * 8;
+      const int src = rows[r];
+      *reinterpret_cast<uint4*>(&As[r][c8]) = (src >= 0 && k0 + c8 < K)
+          ? *reinterpret_cast<const uint4*>(A + (size_t)src * lda + k0 + c8) : zero;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int v = tid + 128 * i, c = v >> 3, c8 = (v & 7) * 8;
+      const int col = SWIGLU ? (c < cols ? n0 + c : n0 + c - cols) : n0 + c;        // the output column this row of the tile feeds
+      const int wrow = SWIGLU && c >= cols ? n_out + col : col;
+      *reinterpret_cast<uint4*>(&Ws[c][c8]) = (col < n_out && k0 + c8 < K)
+          ? *reinterpret_cast<const uint4*>(We + (size_t)wrow * K + k0 + c8) : zero;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      unsigned a[4];
+      a[0] = *reinterpret_cast<const unsigned*>(&As[g][kk + 2 * t]);
+      a[1] = *reinterpret_cast<const unsigned*>(&As[g + 8][kk + 2 * t]);
+      a[2] = *reinterpret_cast<const unsigned*>(&As[g][kk + 8 + 2 * t]);
+      a[3] = *reinterpret_cast<const unsigned*>(&As[g + 8][kk + 8 + 2 * t]);
+      moe_mma_bf16(acc0, a, *reinterpret_cast<const unsigned*>(&Ws[r0][kk + 2 * t]),
+                   *reinterpret_cast<const unsigned*>(&Ws[r0][kk + 8 + 2 * t]));
+      moe_mma_bf16(acc1, a, *reinterpret_cast<const unsigned*>(&Ws[r1][kk + 2 * t]),
+                   *reinterpret_cast<const unsigned*>(&Ws[r1][kk + 8 + 2 * t]));
+    }
+    __syncthreads();
+  }
+  // accumulator layout: [0], [1] = row g, columns 2t and 2t + 1; [2], [3] = row g + 8, the same columns
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = g + 8 * h;
+    if (rows[r] < 0) continue;
+    TO* crow = C + (size_t)(tile * BM + r) * ldc;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      if (SWIGLU) {
+        const int n = n0 + 8 * warp + 2 * t + j;
+        const float gt = acc0[2 * h + j], up = acc1[2 * h + j];
+        if (n < n_out) crow[n] = Num<TO>::from_f(gt / (1.0f + expf(-gt)) * up);
+      } else {
+        const int na = n0 + 16 * warp + 2 * t + j, nb = na + 8;
+        if (na < n_out) crow[na] = Num<TO>::from_f(acc0[2 * h + j]);
+        if (nb < n_out) crow[nb] = Num<TO>::from_f(acc1[2 * h + j]);
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_row, const float* __restrict__ weights,
                    float* __restrict__ out, int hidden, int top) {
@@ -180,6 +268,17 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_row
       acc = fmaf(weights[(size_t)t * top + k], y[(size_t)pair_row[(size_t)t * top + k] * hidden + i], acc);
     out[(size_t)t * hidden + i] = acc;
   }
+}
+
+int launch_products_mma(const void* x, const void* w_gate_up, const void* w_down, const int* tile_expert, const int* sorted_pair,
+                        void* act, float* y, int max_tiles, int hidden, int ff, int top, cudaStream_t stream) {
+  int rc = launch_pdl(moe_product_mma_kernel<bf16, true>, dim3((ff + 31) / 32, max_tiles), dim3(128), 0, stream,
+                      (const bf16*)x, (long long)hidden, top, (const bf16*)w_gate_up, tile_expert, sorted_pair, (bf16*)act,
+                      (long long)ff, ff, hidden);
+  if (rc) return rc;
+  return launch_pdl(moe_product_mma_kernel<float, false>, dim3((hidden + 63) / 64, max_tiles), dim3(128), 0, stream,
+                    (const bf16*)act, (long long)ff, 0, (const bf16*)w_down, tile_expert, sorted_pair, y, (long long)hidden,
+                    hidden, ff);
 }
 
 template <typename T, int TM>
@@ -261,6 +360,9 @@ IFX_API int ifx_moe_experts(const void* x, int dtype, const void* w_gate_up, con
   if (dtype == IFX_F32)
     rc = tile == 16 ? launch_products<float, 1>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream)
                     : launch_products<float, 4>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream);
+  else if (dtype == IFX_BF16 && tile == 16 && hidden % 8 == 0 && ff % 8 == 0 &&
+           (((uintptr_t)x | (uintptr_t)w_gate_up | (uintptr_t)w_down | (uintptr_t)act) & 15) == 0)
+    rc = launch_products_mma(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream);
   else if (dtype == IFX_BF16)
     rc = tile == 16 ? launch_products<bf16, 1>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream)
                     : launch_products<bf16, 4>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream);

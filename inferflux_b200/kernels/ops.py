@@ -146,7 +146,7 @@ def _lib():
         lib.ifx_attn_paged_generic_ex.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int,
                                                   c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                   c_void_p, c_int, c_int, c_int, c_float, c_int,
-                                                  c_int, c_float, c_int, c_int, c_void_p, c_int, c_ll, c_int, c_void_p]
+                                                  c_int, c_float, c_int, c_int, c_void_p, c_int, c_ll, c_int, c_int, c_void_p]
         lib.ifx_attn_prefill_bf16_ex.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int,
                                                  c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                  c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_int, c_int,
@@ -1241,8 +1241,10 @@ def attn_paged_options(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_laye
                        tile_q0: torch.Tensor, n_tiles: int, entry_q_start: torch.Tensor, entry_q_len: torch.Tensor,
                        entry_ctx_start: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float, window: int,
                        v_dim: int, softcap: float = 0.0, keep_first: int = 0, sink: bool = False,
-                       gate: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """:func:`attn_paged_generic` with values ``v_dim`` wide, a cap on the scores (``softcap * tanh(s / softcap)``,
+                       gate: Optional[torch.Tensor] = None, single_tokens: bool = False) -> torch.Tensor:
+    """With ``single_tokens`` every listed tile is one token (``tile_q0`` = its place in its entry) and the kernel
+    for single tokens runs (a block a token and head, its warps sharing the keys out).  Otherwise
+    :func:`attn_paged_generic` with values ``v_dim`` wide, a cap on the scores (``softcap * tanh(s / softcap)``,
     0 = none), ``keep_first`` first tokens that stay visible behind the window, a sink (one more term ``exp(0)`` in
     the denominator) and an output gate: ``gate`` = float32 ``[N, W]`` or ``[P, N, W]`` sums whose first
     ``n_heads * v_dim`` columns go through a sigmoid and multiply the result element by element."""
@@ -1262,7 +1264,8 @@ def attn_paged_options(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_laye
                                             block_tables.stride(0), _ptr(tile_entry), _ptr(tile_q0), n_tiles,
                                             _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_ctx_start),
                                             n_heads, n_kv, head_dim, float(scale), int(window), int(v_dim), float(softcap),
-                                            int(keep_first), 1 if sink else 0, gp, g_parts, g_pstride, g_stride, _stream()),
+                                            int(keep_first), 1 if sink else 0, gp, g_parts, g_pstride, g_stride,
+                                            1 if single_tokens else 0, _stream()),
            "attn_paged_options")
     return out
 

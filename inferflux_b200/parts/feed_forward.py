@@ -183,7 +183,9 @@ class RoutedExperts(Part):
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
-        self.router = Linear(tensors.pop(n("router")).float(), tensors.pop(n("router.b")))     # 32-bit whatever the engine
+        # The router's products are 32-bit whatever the engine: a bfloat16 weight times a bfloat16 input is exact
+        # in float32, and the sums are float32 (the library's product or the weight-streaming kernel).
+        self.router = Linear(tensors.pop(n("router")), tensors.pop(n("router.b")))
         mats = [[tensors.pop(n(f"e{k}.{x}")) for x in ("gate", "up", "down")] for k in range(self.experts)]
         kinds = {m.dtype for row in mats for m in row}
         cast = (lambda m: m.float()) if len(kinds) > 1 else (lambda m: m)

@@ -34,21 +34,21 @@ from .linear import Linear
 
 QUERY_TILE = 16     # tokens per query tile of the plain attention kernel
 CHUNK_TILE = 64     # tokens per query tile of the tensor-core kernel for prompt portions
-CHUNK_MIN = 8       # an entry with at least this many new tokens goes to the tensor-core kernel (where it serves)
+PORTION_MIN = 8     # an entry with fewer new tokens than this is run token by token by the kernel for single tokens
 
 
 @dataclass
 class QueryTiles:
-    """The step's query tiles and the entry of every row: int32 device tensors.  ``tile_*``: tiles of QUERY_TILE
-    tokens over all entries; ``short_*``: the same over the entries with fewer than CHUNK_MIN new tokens (single
-    decoded tokens among them); ``chunk_*``: tiles of CHUNK_TILE tokens over the other entries."""
+    """How the attention kernels see the step, and the entry of every row: int32 device tensors.  ``single_*``: one
+    (entry, place in the entry) per token of the entries with fewer than PORTION_MIN new tokens (decoded tokens
+    among them); ``tile_*`` and ``chunk_*``: the other entries cut into tiles of QUERY_TILE and of CHUNK_TILE tokens."""
 
+    single_entry: torch.Tensor
+    single_q0: torch.Tensor
+    n_single: int
     tile_entry: torch.Tensor
     tile_q0: torch.Tensor
     n_tiles: int
-    short_entry: torch.Tensor
-    short_q0: torch.Tensor
-    n_short: int
     chunk_entry: torch.Tensor
     chunk_q0: torch.Tensor
     n_chunk: int
@@ -56,18 +56,19 @@ class QueryTiles:
 
 
 def describe_query_tiles(layout, put) -> QueryTiles:
-    tile_entry, tile_q0, short_entry, short_q0, chunk_entry, chunk_q0 = [], [], [], [], [], []
+    single_entry, single_q0, tile_entry, tile_q0, chunk_entry, chunk_q0 = [], [], [], [], [], []
     for i in range(layout.n_entries):
         n = int(layout.q_len[i])
+        if n < PORTION_MIN:
+            for q0 in range(n):
+                single_entry.append(i), single_q0.append(q0)
+            continue
         for q0 in range(0, n, QUERY_TILE):
             tile_entry.append(i), tile_q0.append(q0)
-            if n < CHUNK_MIN:
-                short_entry.append(i), short_q0.append(q0)
-        if n >= CHUNK_MIN:
-            for q0 in range(0, n, CHUNK_TILE):
-                chunk_entry.append(i), chunk_q0.append(q0)
+        for q0 in range(0, n, CHUNK_TILE):
+            chunk_entry.append(i), chunk_q0.append(q0)
     rows = np.repeat(np.arange(layout.n_entries), layout.q_len[:layout.n_entries])
-    return QueryTiles(put(tile_entry), put(tile_q0), len(tile_entry), put(short_entry), put(short_q0), len(short_entry),
+    return QueryTiles(put(single_entry), put(single_q0), len(single_entry), put(tile_entry), put(tile_q0), len(tile_entry),
                       put(chunk_entry), put(chunk_q0), len(chunk_entry), put(rows))
 
 
@@ -183,19 +184,17 @@ class WindowAttention(Part):
         gate = proj[:, self._channels(self.params):] if self.gate else None
         common = (ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start, self.heads, self.kv_heads, self.dim, self.scale,
                   self.window)
-        fast = (self.TENSOR_CORES and x.dtype == torch.bfloat16 and self.dim == self.vdim and out.is_contiguous()
-                and self.dim in ops.FAST_ATTENTION_HEAD_DIMS and step.n_chunk > 0)
-        if fast:
-            # prompt portions on tensor cores; the step's short entries (single tokens) stay with the plain kernel
-            ops.attn_prefill_options_bf16(q, q.stride(0), out, k_layer, v_layer, page_stride, ctx.page_size,
-                                          ctx.block_tables[g], step.chunk_entry, step.chunk_q0, step.n_chunk, *common,
-                                          self.softcap, self.keep_first, self.sink, gate)
-            tiles = (step.short_entry, step.short_q0, step.n_short)
-        else:
-            tiles = (step.tile_entry, step.tile_q0, step.n_tiles)
-        if tiles[2]:
-            ops.attn_paged_options(q, q.stride(0), out, k_layer, v_layer, page_stride, ctx.page_size, ctx.block_tables[g],
-                                   *tiles, *common, self.vdim, self.softcap, self.keep_first, self.sink, gate)
+        rest = (self.vdim, self.softcap, self.keep_first, self.sink, gate)
+        pages = (k_layer, v_layer, page_stride, ctx.page_size, ctx.block_tables[g])
+        if step.n_single:       # decoded tokens and the shortest portions: a block a token and head
+            ops.attn_paged_options(q, q.stride(0), out, *pages, step.single_entry, step.single_q0, step.n_single, *common, *rest,
+                                   single_tokens=True)
+        if step.n_chunk and (self.TENSOR_CORES and x.dtype == torch.bfloat16 and self.dim == self.vdim and out.is_contiguous()
+                             and self.dim in ops.FAST_ATTENTION_HEAD_DIMS):
+            ops.attn_prefill_options_bf16(q, q.stride(0), out, *pages, step.chunk_entry, step.chunk_q0, step.n_chunk, *common,
+                                          self.softcap, self.keep_first, self.sink, gate)      # portions on tensor cores
+        elif step.n_tiles:
+            ops.attn_paged_options(q, q.stride(0), out, *pages, step.tile_entry, step.tile_q0, step.n_tiles, *common, *rest)
         return out
 
     def forward(self, x: torch.Tensor, ctx, run: RunInfo, position):
