@@ -395,8 +395,8 @@ class PemoraxConfig(ModelConfig):
                "rot": cls._rot(m, where, dim), "mask": None}
         if heads % out["kv_heads"]:
             raise ConfigError(f"{where}: heads {heads} is not a multiple of kv_heads {out['kv_heads']}")
-        if out["conv"] > 8:
-            raise ConfigError(f"{where}: a convolution of {out['conv']} taps is not supported (at most 8)")
+        if out["conv"] > 16:
+            raise ConfigError(f"{where}: a convolution of {out['conv']} taps is not supported (at most 16)")
         if out["softcap"] is not None and out["softcap"] <= 0:
             raise ConfigError(f"{where}: softcap must be positive")
         mask = _sub(m, "mask", where, optional=True)

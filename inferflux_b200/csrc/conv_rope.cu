@@ -15,7 +15,7 @@
 #include "common.cuh"
 
 namespace {
-constexpr int MAX_TAPS = 8;
+constexpr int MAX_TAPS = 16;
 enum { LAYOUT_HALF = 0, LAYOUT_INTERLEAVED = 1 };
 
 struct ConvRope {

@@ -40,12 +40,16 @@ __device__ __forceinline__ void decay_powers(float* pw, float g, int tid) {
   if (tid <= SEG) pw[tid] = (float)pow((double)g, (double)tid);
 }
 
-// k[j][d] (scaled) with rows of dim + 1, v[j][c] for the block's columns
+// Rows of k in shared memory are `key_ld(dim)` floats apart: dim + 4 where dim is a multiple of 4 (rows stay
+// 16-byte aligned for the vector paths and neighbouring rows fall into different banks), else dim + 1.
+__host__ __device__ __forceinline__ int key_ld(int dim) { return (dim & 3) ? dim + 1 : dim + 4; }
+
+// k[j][d] (scaled), v[j][c] for the block's columns
 __device__ __forceinline__ void load_kv(const RetStep& s, int row0, int n, int head, int v0, float* ks, float* vs, int tid) {
-  const int D = s.dim;
+  const int D = s.dim, KD = key_ld(D);
   for (int idx = tid; idx < SEG * D; idx += THREADS) {
     const int j = idx / D, d = idx - j * D;
-    ks[j * (D + 1) + d] = j < n ? s.proj[(size_t)(row0 + j) * s.stride + s.k_col + head * D + d] * s.k_scale : 0.0f;
+    ks[j * KD + d] = j < n ? s.proj[(size_t)(row0 + j) * s.stride + s.k_col + head * D + d] * s.k_scale : 0.0f;
   }
   for (int idx = tid; idx < SEG * VT; idx += THREADS) {
     const int j = idx / VT, c = idx - j * VT;
@@ -57,11 +61,43 @@ __device__ __forceinline__ void load_kv(const RetStep& s, int row0, int n, int h
 __device__ __forceinline__ void fold_segment(const float* ks, const float* vs, const float* pw, int n, int D, int V, int v0,
                                              const float* old_tile /* smem [D][VT] or null */, float* dst /* global [D][V] */,
                                              int tid) {
+  const int KD = key_ld(D);
+  if (!(D & 3)) {
+    // a thread owns 4 columns and groups of 4 state rows: per token one 16-byte load of keys and one of values
+    const int cg = tid & 15, dg = tid >> 4;
+    for (int grp = dg; grp < D / 4; grp += THREADS / 16) {
+      float acc[4][4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.0f;
+      for (int j = 0; j < n; ++j) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + j * KD + 4 * grp);
+        const float4 v4 = *reinterpret_cast<const float4*>(vs + j * VT + 4 * cg);
+        const float w = pw[n - 1 - j];
+        const float kk[4] = {k4.x * w, k4.y * w, k4.z * w, k4.w * w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+          for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(kk[a], vv[b], acc[a][b]);
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const int d = 4 * grp + a;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int c = 4 * cg + b;
+          if (v0 + c < V) dst[(size_t)d * V + v0 + c] = old_tile ? fmaf(pw[n], old_tile[d * VT + c], acc[a][b]) : acc[a][b];
+        }
+      }
+    }
+    return;
+  }
   const int c = tid % VT, g = tid / VT;
   if (v0 + c >= V) return;
   for (int d = g; d < D; d += GROUPS) {
     float acc = old_tile ? pw[n] * old_tile[d * VT + c] : 0.0f;
-    for (int j = 0; j < n; ++j) acc = fmaf(pw[n - 1 - j] * ks[j * (D + 1) + d], vs[j * VT + c], acc);
+    for (int j = 0; j < n; ++j) acc = fmaf(pw[n - 1 - j] * ks[j * KD + d], vs[j * VT + c], acc);
     dst[(size_t)d * V + v0 + c] = acc;
   }
 }
@@ -71,8 +107,8 @@ retention_segment_sums_kernel(RetStep s, float* __restrict__ seg_b) {
   pdl_enter();
   extern __shared__ float smem[];
   const int D = s.dim, V = s.vdim;
-  float* ks = smem;                        // [SEG][D + 1]
-  float* vs = ks + SEG * (D + 1);          // [SEG][VT]
+  float* ks = smem;                        // [SEG][key_ld(D)]
+  float* vs = ks + SEG * key_ld(D);        // [SEG][VT]
   float* pw = vs + SEG * VT;               // [SEG + 1]
   const int seg = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * VT, tid = threadIdx.x;
   const int e = s.seg_entry[seg], t0 = s.seg_t0[seg];
@@ -112,8 +148,9 @@ retention_outputs_kernel(RetStep s, const float* __restrict__ seg_start, float* 
   pdl_enter();
   extern __shared__ float smem[];
   const int D = s.dim, V = s.vdim;
-  float* ks = smem;                        // [SEG][D + 1]
-  float* vs = ks + SEG * (D + 1);          // [SEG][VT]
+  const int KD = key_ld(D);
+  float* ks = smem;                        // [SEG][KD]
+  float* vs = ks + SEG * KD;               // [SEG][VT]
   float* pw = vs + SEG * VT;               // [SEG + 1] (+ padding to a multiple of 4)
   float* qs = pw + SEG + 4;                // [SEG][D]
   float* St = qs + SEG * D;                // [D][VT]
@@ -136,37 +173,96 @@ retention_outputs_kernel(RetStep s, const float* __restrict__ seg_start, float* 
   }
   __syncthreads();
   // decayed scores of the segment: P[i][j] = g^(i-j) (q_i . k_j) for j <= i
-  for (int idx = tid; idx < SEG * SEG; idx += THREADS) {
-    const int i = idx / SEG, j = idx - i * SEG;
-    float dot = 0.0f;
-    if (j <= i && i < n) {
-      const float* qa = qs + i * D;
-      const float* kb = ks + j * (D + 1);
-      for (int d = 0; d < D; ++d) dot = fmaf(qa[d], kb[d], dot);
-      dot *= pw[i - j];
+  if (!(D & 3)) {
+    // a thread takes rows bi, bi + 16 against keys bj, bj + 16: four dot products from 16-byte loads
+    const int bi = tid >> 4, bj = tid & 15;
+    float d00 = 0.0f, d01 = 0.0f, d10 = 0.0f, d11 = 0.0f;
+    for (int d = 0; d < D; d += 4) {
+      const float4 qa = *reinterpret_cast<const float4*>(qs + bi * D + d), qb = *reinterpret_cast<const float4*>(qs + (bi + 16) * D + d);
+      const float4 ka = *reinterpret_cast<const float4*>(ks + bj * KD + d), kb = *reinterpret_cast<const float4*>(ks + (bj + 16) * KD + d);
+      d00 = fmaf(qa.x, ka.x, fmaf(qa.y, ka.y, fmaf(qa.z, ka.z, fmaf(qa.w, ka.w, d00))));
+      d01 = fmaf(qa.x, kb.x, fmaf(qa.y, kb.y, fmaf(qa.z, kb.z, fmaf(qa.w, kb.w, d01))));
+      d10 = fmaf(qb.x, ka.x, fmaf(qb.y, ka.y, fmaf(qb.z, ka.z, fmaf(qb.w, ka.w, d10))));
+      d11 = fmaf(qb.x, kb.x, fmaf(qb.y, kb.y, fmaf(qb.z, kb.z, fmaf(qb.w, kb.w, d11))));
     }
-    P[i * (SEG + 1) + j] = dot;
+    const int i0 = bi, i1 = bi + 16, j0 = bj, j1 = bj + 16;
+    P[i0 * (SEG + 1) + j0] = (j0 <= i0 && i0 < n) ? d00 * pw[i0 - j0] : 0.0f;
+    P[i0 * (SEG + 1) + j1] = 0.0f;                                   // j1 >= 16 > i0
+    P[i1 * (SEG + 1) + j0] = i1 < n ? d10 * pw[i1 - j0] : 0.0f;      // j0 < 16 <= i1
+    P[i1 * (SEG + 1) + j1] = (j1 <= i1 && i1 < n) ? d11 * pw[i1 - j1] : 0.0f;
+  } else {
+    for (int idx = tid; idx < SEG * SEG; idx += THREADS) {
+      const int i = idx / SEG, j = idx - i * SEG;
+      float dot = 0.0f;
+      if (j <= i && i < n) {
+        const float* qa = qs + i * D;
+        const float* kb = ks + j * KD;
+        for (int d = 0; d < D; ++d) dot = fmaf(qa[d], kb[d], dot);
+        dot *= pw[i - j];
+      }
+      P[i * (SEG + 1) + j] = dot;
+    }
   }
   __syncthreads();
-  const int c = tid % VT, g = tid / VT;
-  float inter[TPT], intra[TPT];
+  if (!(D & 3)) {
+    // a thread owns tokens tg, tg + 16 and 4 columns: per 4 state rows four 16-byte loads of the state and two of q
+    const int cg = tid & 15, tg = tid >> 4;
+    float inter[2][4], intra[2][4];
 #pragma unroll
-  for (int u = 0; u < TPT; ++u) { inter[u] = 0.0f; intra[u] = 0.0f; }
-  for (int d = 0; d < D; ++d) {
-    const float sv = St[d * VT + c];
+    for (int a = 0; a < 2; ++a)
 #pragma unroll
-    for (int u = 0; u < TPT; ++u) inter[u] = fmaf(qs[(g + GROUPS * u) * D + d], sv, inter[u]);
-  }
-  for (int j = 0; j < n; ++j) {
-    const float vv = vs[j * VT + c];
+      for (int b = 0; b < 4; ++b) { inter[a][b] = 0.0f; intra[a][b] = 0.0f; }
+    for (int d = 0; d < D; d += 4) {
+      const float4 qa = *reinterpret_cast<const float4*>(qs + tg * D + d), qb = *reinterpret_cast<const float4*>(qs + (tg + 16) * D + d);
+      const float qv[2][4] = {{qa.x, qa.y, qa.z, qa.w}, {qb.x, qb.y, qb.z, qb.w}};
 #pragma unroll
-    for (int u = 0; u < TPT; ++u) intra[u] = fmaf(P[(g + GROUPS * u) * (SEG + 1) + j], vv, intra[u]);
-  }
-  if (v0 + c < V) {
+      for (int u = 0; u < 4; ++u) {
+        const float4 s4 = *reinterpret_cast<const float4*>(St + (d + u) * VT + 4 * cg);
+        const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
-    for (int u = 0; u < TPT; ++u) {
-      const int i = g + GROUPS * u;
-      if (i < n) out[(size_t)(row0 + i) * s.heads * V + (size_t)head * V + v0 + c] = fmaf(pw[i + 1], inter[u], intra[u]);
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+          for (int b = 0; b < 4; ++b) inter[a][b] = fmaf(qv[a][u], sv[b], inter[a][b]);
+      }
+    }
+    for (int j = 0; j < n; ++j) {
+      const float4 v4 = *reinterpret_cast<const float4*>(vs + j * VT + 4 * cg);
+      const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+      const float pa = P[tg * (SEG + 1) + j], pb = P[(tg + 16) * (SEG + 1) + j];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) { intra[0][b] = fmaf(pa, vv[b], intra[0][b]); intra[1][b] = fmaf(pb, vv[b], intra[1][b]); }
+    }
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      const int i = tg + 16 * a;
+      if (i >= n) continue;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int c = 4 * cg + b;
+        if (v0 + c < V) out[(size_t)(row0 + i) * s.heads * V + (size_t)head * V + v0 + c] = fmaf(pw[i + 1], inter[a][b], intra[a][b]);
+      }
+    }
+  } else {
+    const int c = tid % VT, g = tid / VT;
+    float inter[TPT], intra[TPT];
+#pragma unroll
+    for (int u = 0; u < TPT; ++u) { inter[u] = 0.0f; intra[u] = 0.0f; }
+    for (int d = 0; d < D; ++d) {
+      const float sv = St[d * VT + c];
+#pragma unroll
+      for (int u = 0; u < TPT; ++u) inter[u] = fmaf(qs[(g + GROUPS * u) * D + d], sv, inter[u]);
+    }
+    for (int j = 0; j < n; ++j) {
+      const float vv = vs[j * VT + c];
+#pragma unroll
+      for (int u = 0; u < TPT; ++u) intra[u] = fmaf(P[(g + GROUPS * u) * (SEG + 1) + j], vv, intra[u]);
+    }
+    if (v0 + c < V) {
+#pragma unroll
+      for (int u = 0; u < TPT; ++u) {
+        const int i = g + GROUPS * u;
+        if (i < n) out[(size_t)(row0 + i) * s.heads * V + (size_t)head * V + v0 + c] = fmaf(pw[i + 1], inter[u], intra[u]);
+      }
     }
   }
   if (!seg_start) fold_segment(ks, vs, pw, n, D, V, v0, St, slot_tile, tid);   // every thread writes only what it read
@@ -194,7 +290,7 @@ retention_finish_kernel(const float* __restrict__ o, const float* __restrict__ g
 }
 
 size_t outputs_smem(int D) {
-  return ((size_t)SEG * (D + 1) + SEG * VT + SEG + 4 + (size_t)SEG * D + (size_t)D * VT + SEG * (SEG + 1)) * sizeof(float);
+  return ((size_t)SEG * key_ld(D) + SEG * VT + SEG + 4 + (size_t)SEG * D + (size_t)D * VT + SEG * (SEG + 1)) * sizeof(float);
 }
 }  // namespace
 
@@ -223,7 +319,7 @@ IFX_API int ifx_retention_scan(const float* proj, int stride, int q_col, int k_c
   }
   int rc;
   if (multi) {
-    const size_t smem_a = ((size_t)SEG * (dim + 1) + SEG * VT + SEG + 4) * sizeof(float);
+    const size_t smem_a = ((size_t)SEG * key_ld(dim) + SEG * VT + SEG + 4) * sizeof(float);
     rc = launch_pdl(retention_segment_sums_kernel, dim3(n_segments, heads, vtiles), dim3(THREADS), smem_a, stream, s, seg_b);
     if (rc) return rc;
     const int zb = (int)(((size_t)dim * vdim + 4 * THREADS - 1) / (4 * THREADS));

@@ -73,7 +73,7 @@ def describe_query_tiles(layout, put) -> QueryTiles:
 
 
 class WindowAttention(Part):
-    """params: ``hidden``, ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``conv`` (taps, 0 or 1 = none), ``rot_dims``,
+    """params: ``hidden``, ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``conv`` (taps, 0 = none), ``rot_dims``,
     ``rot_layout`` (``interleaved`` or ``half``), ``scale`` (None = ``dim^-1/2``), ``softcap`` (None = none),
     ``window`` (None = all keys), ``keep_first``, ``sink``, ``gate``, ``name``.  Tensors
     ``<prefix>.<name>.{q,k,v,g,o}`` and ``<prefix>.<name>.{q,k,v}.conv`` ``[channels, taps]``.
@@ -105,8 +105,8 @@ class WindowAttention(Part):
             raise ValueError(f"rot_dims {self.rot_dims} must be even and at most dim {self.dim}")
         if not (1 <= self.dim <= 256 and 1 <= self.vdim <= 256):
             raise ValueError("dim and vdim must be within 1..256")
-        if self.taps > 8:
-            raise ValueError("a convolution of more than 8 taps is not built")
+        if self.taps > 16:
+            raise ValueError("a convolution of more than 16 taps is not built")
         self.qkvg: Linear = None
         self.conv_w: Optional[torch.Tensor] = None
         self.o: Linear = None
@@ -122,7 +122,7 @@ class WindowAttention(Part):
         rows = {"q": nh * d, "k": nkv * d, "v": nkv * vd}
         specs = [WeightSpec(n(x), (r, h), MATRIX) for x, r in rows.items()]
         taps = int(params.get("conv") or 0)
-        if taps > 1:
+        if taps >= 1:                       # one tap is a weight per channel and no reach back in time
             specs += [WeightSpec(n(f"{x}.conv"), (r, taps), VECTOR, std=0.5) for x, r in rows.items()]
         if params.get("gate"):
             specs.append(WeightSpec(n("g"), (nh * vd, h), MATRIX))
@@ -148,7 +148,7 @@ class WindowAttention(Part):
             mats = [m.float() for m in mats]
         self.qkvg = Linear(torch.cat(mats, dim=0))
         del mats
-        if self.taps > 1:
+        if self.taps >= 1:
             self.conv_w = torch.cat([tensors.pop(n(f"{x}.conv")).float() for x in ("q", "k", "v")]).contiguous()
         self.o = Linear(tensors.pop(n("o")))
 

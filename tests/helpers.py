@@ -225,13 +225,14 @@ PX_A = dict(architecture="Pemorax", width=64, vocab=300, norm=dict(eps=1e-5), la
     _px_layer(_px_left(2, 2, 32, 32, conv=2, mask=dict(size=33, keep_first=0), rot=dict(dims=32, base=300.0)),
               _px_right(1, 16, 8, [0.95], rot=dict(dims=4, base=100.0)), _MOE(40, 5, 2)),
     _px_layer(_px_left(3, 1, 8, 4), _px_right(2, 8, 8, [0.5, 0.99]), None)])
-# B: sizes that are no multiple of 4 or 8 anywhere, a window shorter than a page, every expert chosen, one expert of three
+# B: sizes that are no multiple of 4 or 8 anywhere, a window shorter than a page, every expert chosen, one expert of
+# three, convolutions of eight taps and of one
 PX_B = dict(architecture="Pemorax", width=50, vocab=77, norm=dict(eps=3e-6), layers=[
     _px_layer(_px_left(3, 3, 10, 6, conv=3, mask=dict(size=7, keep_first=1), rot=dict(dims=6, base=50.0), softcap=3.0),
               _px_right(2, 6, 10, [0.8, 0.999], rot=dict(dims=6, base=1000.0)), _MOE(35, 3, 3)),
     _px_layer(_px_left(5, 1, 6, 10, conv=8, mask=dict(size=40, keep_first=18), rot=dict(dims=2, base=20.0)),
               _px_right(5, 10, 6, [0.7, 0.9, 0.95, 0.99, 0.995], rot=dict(dims=10, base=7.0)), _MOE(18, 3, 1)),
-    _px_layer(_px_left(1, 1, 14, 14, conv=2, mask=dict(size=64, keep_first=64)), _px_right(1, 14, 2, [0.96]), dict(kind="dense", ff=45))])
+    _px_layer(_px_left(1, 1, 14, 14, conv=1, mask=dict(size=64, keep_first=64)), _px_right(1, 14, 2, [0.96]), dict(kind="dense", ff=45))])
 # C: heads of 64 and of 128 (the sizes tensor-core kernels take), windows longer than several pages, many experts
 PX_C = dict(architecture="Pemorax", width=128, vocab=200, norm=dict(eps=1e-6), layers=[
     _px_layer(_px_left(4, 2, 64, 64, conv=4, mask=dict(size=70, keep_first=5), rot=dict(dims=64, base=250000.0, scaling=_YARN),

@@ -109,7 +109,7 @@ def left_mixer(h, w, p, m):
     proj = {}
     for x in ("q", "k", "v"):
         u = h @ w[f"{p}.{x}"].T
-        proj[x] = short_conv(u, w[f"{p}.{x}.conv"])[0] if m.get("conv", 0) > 1 else u
+        proj[x] = short_conv(u, w[f"{p}.{x}.conv"])[0] if m.get("conv", 0) >= 1 else u
     q = rotate(proj["q"].view(t, m["heads"], m["dim"]), pos, m.get("rot"), True)
     k = rotate(proj["k"].view(t, m["kv_heads"], m["dim"]), pos, m.get("rot"), True)
     v = proj["v"].view(t, m["kv_heads"], m["vdim"])
