@@ -293,7 +293,10 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
           for (int c = 0; c < 4; ++c) s[n][c] = opt.softcap * tanh_exp(s[n][c] * cap_in);
         }
       }
-      const bool need_mask = key0 + BK - 1 > pos0 + wr0 || window > 0 || key0 < kfirst;
+      // a tile needs no mask when every row of the warp sees all of it: it ends at or before the warp's first
+      // position and starts inside the window of the warp's last one (or lies wholly among the kept first tokens)
+      const bool need_mask = key0 + BK - 1 > pos0 + wr0 || key0 + BK > kend ||
+                             (window > 0 && key0 <= pos0 + wr0 + 15 - window && key0 + BK > keep);
       if (need_mask) {
 #pragma unroll
         for (int n = 0; n < BK / 8; ++n) {

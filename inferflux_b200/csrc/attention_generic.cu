@@ -179,7 +179,7 @@ attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __rest
 // Single tokens: one block a (token, head), its warps take the key tiles of 32 in turn (a lane a key for the
 // scores, a lane a few value dimensions for the sum), each warp with a running maximum, sum and result of its
 // own that the block merges at the end; keys and values are read straight from the pages.  The same options.
-constexpr int DEC_WARPS = 8;
+constexpr int DEC_WARPS = 16;
 
 template <typename T, int NACC>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
@@ -210,6 +210,10 @@ attn_single_token_kernel(const T* __restrict__ q, long long q_stride, T* __restr
   float m = -INFINITY, l = 0.0f, o[NACC];
 #pragma unroll
   for (int a = 0; a < NACC; ++a) o[a] = 0.0f;
+  // which value dimension accumulator a of this lane holds: lane + 32 a, or, where a lane can take 4 neighbouring
+  // 16-bit values with one 8-byte load (values 128 or 256 wide), 4 lane + (a mod 4) + 128 (a / 4)
+  const bool vec_v = sizeof(T) == 2 && NACC >= 4 && v_dim == 32 * NACC && kv.page_size >= 4;
+#define IFX_DIM_OF(a) (vec_v ? 4 * lane + ((a) & 3) + 128 * ((a) >> 2) : lane + 32 * (a))
   for (int it = warp; it < n_tiles; it += DEC_WARPS) {
     const int k0 = it < n_keep ? it * BKEYS : kstart + (it - n_keep) * BKEYS;
     const int key = k0 + lane;
@@ -249,19 +253,33 @@ attn_single_token_kernel(const T* __restrict__ q, long long q_stride, T* __restr
       const int pg = __shfl_sync(0xffffffffu, page, j);
       if (pjj == 0.0f) continue;                      // warp-uniform; keeps stale values out
       const T* vr = vc + (size_t)pg * kv.page_stride + (size_t)((k0 + j) & (kv.page_size - 1)) * v_dim;
+      if (vec_v) {
 #pragma unroll
-      for (int a = 0; a < NACC; ++a) {
-        const int d = lane + 32 * a;
-        if (d < v_dim) o[a] = fmaf(pjj, Num<T>::to_f(vr[d]), o[a]);
+        for (int a4 = 0; a4 < NACC / 4; ++a4) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(vr + 4 * lane + 128 * a4);
+          const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+          const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+          o[4 * a4] = fmaf(pjj, lo.x, o[4 * a4]);
+          o[4 * a4 + 1] = fmaf(pjj, lo.y, o[4 * a4 + 1]);
+          o[4 * a4 + 2] = fmaf(pjj, hi.x, o[4 * a4 + 2]);
+          o[4 * a4 + 3] = fmaf(pjj, hi.y, o[4 * a4 + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) {
+          const int d = lane + 32 * a;
+          if (d < v_dim) o[a] = fmaf(pjj, Num<T>::to_f(vr[d]), o[a]);
+        }
       }
     }
   }
   if (lane == 0) { wm[warp] = m; wl[warp] = l; }
 #pragma unroll
   for (int a = 0; a < NACC; ++a) {
-    const int d = lane + 32 * a;
+    const int d = IFX_DIM_OF(a);
     if (d < v_dim) wo[warp * v_dim + d] = o[a];
   }
+#undef IFX_DIM_OF
   __syncthreads();
   if (warp == 0) {                                    // the merge: warps in index order, the sink as one more term exp(0)
     float mm = opt.sink ? 0.0f : -INFINITY;

@@ -103,6 +103,92 @@ conv_rope_kv_write_kernel(ConvRope p) {
   }
 }
 
+// The same for sizes that allow 16-byte accesses (dim, vdim, the rotated dimensions and the projection's row
+// length multiples of 4): a thread takes 4 neighbouring channels, reads each of the `taps` rows with one float4,
+// and stores its 4 results at once.  Interleaved pairs lie inside the thread's 4 channels; pairs split in halves
+// take the partner's 4 channels from a second set of loads.  The grid's second dimension cuts the channels, so
+// a step of few tokens still fills the GPU.
+__device__ __forceinline__ float4 proj4_at(const ConvRope& p, int row, int c) {
+  float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int s = 0; s < p.parts; ++s) {
+    const float4 u = *reinterpret_cast<const float4*>(p.proj + (size_t)s * p.part_stride + (size_t)row * p.proj_stride + c);
+    v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+  }
+  return v;
+}
+
+__device__ __forceinline__ float4 conv4_at(const ConvRope& p, int row, int i, int slot, int channels, int c) {
+  if (!p.conv_w) return proj4_at(p, row, c);
+  float4 y = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  const float* w = p.conv_w + (size_t)c * p.taps;
+  for (int j = 0; j < p.taps; ++j) {
+    const int m = i - (p.taps - 1) + j;
+    const float4 u = m >= 0 ? proj4_at(p, row - (i - m), c)
+                            : *reinterpret_cast<const float4*>(p.tail + ((size_t)slot * (p.taps - 1) + (p.taps - 1 + m)) * channels + c);
+    y.x = fmaf(w[j], u.x, y.x);
+    y.y = fmaf(w[p.taps + j], u.y, y.y);
+    y.z = fmaf(w[2 * p.taps + j], u.z, y.z);
+    y.w = fmaf(w[3 * p.taps + j], u.w, y.w);
+  }
+  return y;
+}
+
+template <typename T> __device__ __forceinline__ void store4(T* dst, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+template <> __device__ __forceinline__ void store4<bf16>(bf16* dst, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned*>(&lo);
+  raw.y = *reinterpret_cast<unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = raw;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+conv_rope_kv_write_vec_kernel(ConvRope p) {
+  pdl_enter();
+  const int t = blockIdx.x;
+  const int e = p.row_entry[t];
+  const int i = t - p.entry_q_start[e];
+  const int slot = p.entry_slot[e];
+  const int cq = p.n_heads * p.dim, ck = p.n_kv * p.dim, cv = p.n_kv * p.vdim;
+  const int channels = cq + ck + cv;
+  const float* ct = p.cos_t + (size_t)t * p.rot_half;
+  const float* st = p.sin_t + (size_t)t * p.rot_half;
+  const int where = p.slot_map ? p.slot_map[t] : -1;
+  const long long page = where >= 0 ? (where >> p.page_shift) : 0;
+  const int off = where & (p.page_size - 1);
+  const int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
+  if (c >= channels) return;
+  float4 y = conv4_at(p, t, i, slot, channels, c);
+  if (c < cq + ck) {
+    const int head = c / p.dim, d = c - head * p.dim;
+    if (d < 2 * p.rot_half) {
+      if (p.layout == LAYOUT_INTERLEAVED) {                // pairs (d, d + 1) and (d + 2, d + 3)
+        const float c0 = ct[d >> 1], s0 = st[d >> 1], c1 = ct[(d >> 1) + 1], s1 = st[(d >> 1) + 1];
+        y = make_float4(y.x * c0 - y.y * s0, y.y * c0 + y.x * s0, y.z * c1 - y.w * s1, y.w * c1 + y.z * s1);
+      } else {                                             // pairs (d, d + half): the partner's 4 channels
+        const bool first = d < p.rot_half;
+        const int pair = first ? d : d - p.rot_half;
+        const float4 z = conv4_at(p, t, i, slot, channels, head * p.dim + (first ? d + p.rot_half : d - p.rot_half));
+        const float4 co = *reinterpret_cast<const float4*>(ct + pair), si = *reinterpret_cast<const float4*>(st + pair);
+        y = first ? make_float4(y.x * co.x - z.x * si.x, y.y * co.y - z.y * si.y, y.z * co.z - z.z * si.z, y.w * co.w - z.w * si.w)
+                  : make_float4(y.x * co.x + z.x * si.x, y.y * co.y + z.y * si.y, y.z * co.z + z.z * si.z, y.w * co.w + z.w * si.w);
+      }
+    }
+    if (c < cq) {
+      store4<T>((T*)p.q_out + (size_t)t * cq + c, y);
+    } else if (where >= 0) {
+      const int kh = head - p.n_heads;
+      store4<T>((T*)p.k_cache + (size_t)page * p.page_stride + ((size_t)kh * p.page_size + off) * p.dim + d, y);
+    }
+  } else if (where >= 0) {
+    const int cc = c - cq - ck;
+    const int vh = cc / p.vdim, d = cc - vh * p.vdim;
+    store4<T>((T*)p.v_cache + (size_t)page * p.page_stride + ((size_t)vh * p.page_size + off) * p.vdim + d, y);
+  }
+}
+
 // After the rows have been read: the tail becomes the last taps-1 rows of (old tail ++ the entry's new rows).
 __global__ void __launch_bounds__(256)
 conv_tail_update_kernel(ConvRope p) {
@@ -164,8 +250,22 @@ IFX_API int ifx_conv_rope_kv_write(const float* proj, int parts, long long part_
              entry_slot, cos_t, sin_t, rot_half, layout, n_heads, n_kv, dim, vdim, q_out, slot_map, k_cache, v_cache,
              page_stride, page_size, 0};
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
-  int rc = dtype == IFX_BF16 ? launch_pdl(conv_rope_kv_write_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, p)
-                             : launch_pdl(conv_rope_kv_write_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, p);
+  const int all = n_heads * dim + n_kv * dim + n_kv * vdim;
+  // 16-byte accesses: sizes multiples of 4 (of 8 where the rotation pairs halves, so a thread's 4 channels stay
+  // in one half and its cos/sin are 4 aligned floats), aligned pointers
+  const bool vec = !(dim & 3) && !(vdim & 3) && !(proj_stride & 3) && !(part_stride & 3) &&
+                   (layout == LAYOUT_INTERLEAVED ? !(rot_half & 1) : !(rot_half & 3)) && !(page_stride & 3) &&
+                   !(((uintptr_t)proj | (uintptr_t)tail | (uintptr_t)cos_t | (uintptr_t)sin_t | (uintptr_t)q_out |
+                      (uintptr_t)k_cache | (uintptr_t)v_cache) & 15);
+  int rc;
+  if (vec) {
+    const dim3 grid(n_tokens, (all / 4 + 127) / 128);
+    rc = dtype == IFX_BF16 ? launch_pdl(conv_rope_kv_write_vec_kernel<bf16>, grid, dim3(128), 0, stream, p)
+                           : launch_pdl(conv_rope_kv_write_vec_kernel<float>, grid, dim3(128), 0, stream, p);
+  } else {
+    rc = dtype == IFX_BF16 ? launch_pdl(conv_rope_kv_write_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, p)
+                           : launch_pdl(conv_rope_kv_write_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, p);
+  }
   if (rc) return rc;
   if (conv_w && taps > 1) {
     const int channels = n_heads * dim + n_kv * dim + n_kv * vdim;

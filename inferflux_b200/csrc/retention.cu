@@ -132,10 +132,19 @@ retention_carry_kernel(RetStep s, const int* __restrict__ entry_first_seg, const
   float* st = s.state + ((size_t)s.entry_slot[e] * s.heads + head) * tile;
   for (size_t at = (size_t)blockIdx.z * THREADS + threadIdx.x; at < tile; at += (size_t)gridDim.z * THREADS) {
     float S = st[at];
-    for (int k = 0; k < n_seg; ++k) {
-      const size_t o = ((size_t)(seg0 + k) * s.heads + head) * tile + at;
-      seg_start[o] = S;
-      S = fmaf(k == n_seg - 1 ? g_last : g_full, S, seg_b[o]);
+    const size_t step = (size_t)s.heads * tile;
+    const size_t o0 = ((size_t)seg0 * s.heads + head) * tile + at;
+    for (int k0 = 0; k0 < n_seg; k0 += 8) {        // eight segments' sums are asked for before the first is used
+      float bs[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) bs[u] = k0 + u < n_seg ? seg_b[o0 + (size_t)(k0 + u) * step] : 0.0f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int k = k0 + u;
+        if (k >= n_seg) break;
+        seg_start[o0 + (size_t)k * step] = S;
+        S = fmaf(k == n_seg - 1 ? g_last : g_full, S, bs[u]);
+      }
     }
     st[at] = S;
   }
