@@ -179,7 +179,7 @@ attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __rest
 // Single tokens: one block a (token, head), its warps take the key tiles of 32 in turn (a lane a key for the
 // scores, a lane a few value dimensions for the sum), each warp with a running maximum, sum and result of its
 // own that the block merges at the end; keys and values are read straight from the pages.  The same options.
-constexpr int DEC_WARPS = 16;
+constexpr int DEC_WARPS = 32;
 
 template <typename T, int NACC>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
@@ -224,16 +224,19 @@ attn_single_token_kernel(const T* __restrict__ q, long long q_stride, T* __restr
       const T* kr = kc + (size_t)page * kv.page_stride + (size_t)(key & (kv.page_size - 1)) * head_dim;
       float dot = 0.0f;
       if (sizeof(T) == 2 && (head_dim & 7) == 0 && kv.page_size >= 8) {
+        // the key row's 16-byte pieces are asked for eight at a time, and added up in two chains
+        float dot2 = 0.0f;
+#pragma unroll 8
         for (int d = 0; d < head_dim; d += 8) {
           const uint4 raw = *reinterpret_cast<const uint4*>(kr + d);
           const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float2 f = __bfloat1622float2(h2[u]);
-            dot = fmaf(qs[d + 2 * u], f.x, dot);
-            dot = fmaf(qs[d + 2 * u + 1], f.y, dot);
-          }
+          const float4 qa = *reinterpret_cast<const float4*>(qs + d), qb = *reinterpret_cast<const float4*>(qs + d + 4);
+          const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
+          const float2 f2 = __bfloat1622float2(h2[2]), f3 = __bfloat1622float2(h2[3]);
+          dot = fmaf(qa.x, f0.x, fmaf(qa.y, f0.y, fmaf(qa.z, f1.x, fmaf(qa.w, f1.y, dot))));
+          dot2 = fmaf(qb.x, f2.x, fmaf(qb.y, f2.y, fmaf(qb.z, f3.x, fmaf(qb.w, f3.y, dot2))));
         }
+        dot += dot2;
       } else {
         for (int d = 0; d < head_dim; ++d) dot = fmaf(qs[d], Num<T>::to_f(kr[d]), dot);
       }
@@ -248,27 +251,47 @@ attn_single_token_kernel(const T* __restrict__ q, long long q_stride, T* __restr
     m = m_new;
 #pragma unroll
     for (int a = 0; a < NACC; ++a) o[a] *= alpha;
-    for (int j = 0; j < BKEYS; ++j) {
-      const float pjj = __shfl_sync(0xffffffffu, pj, j);
-      const int pg = __shfl_sync(0xffffffffu, page, j);
-      if (pjj == 0.0f) continue;                      // warp-uniform; keeps stale values out
-      const T* vr = vc + (size_t)pg * kv.page_stride + (size_t)((k0 + j) & (kv.page_size - 1)) * v_dim;
-      if (vec_v) {
+    // No branch on the weight here: the values of eight keys are asked for together, from an address that is
+    // always valid (page 0 stands in for a key that is not visible), and what was read for a key of weight 0 is
+    // replaced by zeros before it is used, so stale pages stay out.
+    if (vec_v) {
+      for (int j0 = 0; j0 < BKEYS; j0 += 8) {
+        uint2 raw[8][NACC / 4 > 0 ? NACC / 4 : 1];
+        float wj[8];
 #pragma unroll
-        for (int a4 = 0; a4 < NACC / 4; ++a4) {
-          const uint2 raw = *reinterpret_cast<const uint2*>(vr + 4 * lane + 128 * a4);
-          const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-          const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-          o[4 * a4] = fmaf(pjj, lo.x, o[4 * a4]);
-          o[4 * a4 + 1] = fmaf(pjj, lo.y, o[4 * a4 + 1]);
-          o[4 * a4 + 2] = fmaf(pjj, hi.x, o[4 * a4 + 2]);
-          o[4 * a4 + 3] = fmaf(pjj, hi.y, o[4 * a4 + 3]);
+        for (int u = 0; u < 8; ++u) {
+          wj[u] = __shfl_sync(0xffffffffu, pj, j0 + u);
+          const int pg = __shfl_sync(0xffffffffu, page, j0 + u);
+          const T* vr = vc + (size_t)(wj[u] != 0.0f ? pg : 0) * kv.page_stride + (size_t)((k0 + j0 + u) & (kv.page_size - 1)) * v_dim;
+#pragma unroll
+          for (int a4 = 0; a4 < NACC / 4; ++a4) raw[u][a4] = *reinterpret_cast<const uint2*>(vr + 4 * lane + 128 * a4);
         }
-      } else {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+#pragma unroll
+          for (int a4 = 0; a4 < NACC / 4; ++a4) {
+            const uint2 r2 = wj[u] != 0.0f ? raw[u][a4] : make_uint2(0u, 0u);
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r2.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r2.y));
+            o[4 * a4] = fmaf(wj[u], lo.x, o[4 * a4]);
+            o[4 * a4 + 1] = fmaf(wj[u], lo.y, o[4 * a4 + 1]);
+            o[4 * a4 + 2] = fmaf(wj[u], hi.x, o[4 * a4 + 2]);
+            o[4 * a4 + 3] = fmaf(wj[u], hi.y, o[4 * a4 + 3]);
+          }
+        }
+      }
+    } else {
+#pragma unroll 4
+      for (int j = 0; j < BKEYS; ++j) {
+        const float pjj = __shfl_sync(0xffffffffu, pj, j);
+        const int pg = __shfl_sync(0xffffffffu, page, j);
+        const bool on = pjj != 0.0f;
+        const T* vr = vc + (size_t)(on ? pg : 0) * kv.page_stride + (size_t)((k0 + j) & (kv.page_size - 1)) * v_dim;
 #pragma unroll
         for (int a = 0; a < NACC; ++a) {
           const int d = lane + 32 * a;
-          if (d < v_dim) o[a] = fmaf(pjj, Num<T>::to_f(vr[d]), o[a]);
+          const float vv = d < v_dim ? Num<T>::to_f(vr[d]) : 0.0f;
+          o[a] = fmaf(pjj, on ? vv : 0.0f, o[a]);
         }
       }
     }
