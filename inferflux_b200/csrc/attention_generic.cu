@@ -179,9 +179,9 @@ attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __rest
 // Single tokens: one block a (token, head), its warps take the key tiles of 32 in turn (a lane a key for the
 // scores, a lane a few value dimensions for the sum), each warp with a running maximum, sum and result of its
 // own that the block merges at the end; keys and values are read straight from the pages.  The same options.
-constexpr int DEC_WARPS = 32;
-
-template <typename T, int NACC>
+// DEC_WARPS warps a block: 32 where the step's blocks are few (every warp then has about one tile of a window of
+// 1,024), 16 where they are many (two blocks share an SM and one's merge overlaps the other's tiles).
+template <typename T, int NACC, int DEC_WARPS>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_single_token_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long out_stride,
                          PagedKV kv, AttnBatch b, int n_heads, int n_kv, int head_dim, float scale, int window,
@@ -330,13 +330,26 @@ attn_single_token_kernel(const T* __restrict__ q, long long q_stride, T* __restr
   }
 }
 
+template <typename T, int NACC, int DEC_WARPS>
+int launch_single_w(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnBatch b,
+                    int n_tiles, int n_heads, int n_kv, int head_dim, float scale, int window, AttnOptions opt, cudaStream_t stream) {
+  const size_t smem = ((size_t)head_dim + 2 * DEC_WARPS + (size_t)DEC_WARPS * opt.v_dim) * sizeof(float);
+  const int rc = launch_pdl(attn_single_token_kernel<T, NACC, DEC_WARPS>, dim3(n_tiles, n_heads), dim3(DEC_WARPS * 32), smem, stream,
+                            (const T*)q, q_stride, (T*)out, out_stride, kv, b, n_heads, n_kv, head_dim, scale, window, opt);
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
 template <typename T, int NACC>
 int launch_single(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnBatch b,
                   int n_tiles, int n_heads, int n_kv, int head_dim, float scale, int window, AttnOptions opt, cudaStream_t stream) {
-  const size_t smem = ((size_t)head_dim + 2 * DEC_WARPS + (size_t)DEC_WARPS * opt.v_dim) * sizeof(float);
-  const int rc = launch_pdl(attn_single_token_kernel<T, NACC>, dim3(n_tiles, n_heads), dim3(DEC_WARPS * 32), smem, stream,
-                            (const T*)q, q_stride, (T*)out, out_stride, kv, b, n_heads, n_kv, head_dim, scale, window, opt);
-  return rc ? rc : IFX_LAUNCH_CHECK();
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
+  }
+  if ((long long)n_tiles * n_heads <= 2ll * sms)
+    return launch_single_w<T, NACC, 32>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
+  return launch_single_w<T, NACC, 16>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
 }
 
 template <typename T>
