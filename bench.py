@@ -191,10 +191,10 @@ def pemorax_config(size: str, layers: int):
     width) and 16 experts of a quarter of that width of which a token takes 4 (as many active weights)."""
     _, hidden, heads, kv_heads, inter, vocab, _ = SIZES[size]
     left = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, conv=4, mask=dict(size=1024, keep_first=4),
-                rot=dict(dims=128, base=1000000.0, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)),
-                scale=128 ** -0.5, softcap=50.0)
+                rot=dict(dims=128, base=500000.0, scaling=dict(factor=4.0, original=8192, fast=16.0, slow=2.0)),
+                scale=128 ** -0.5, softcap=30.0)
     rheads = max(1, heads // 2)
-    right = dict(heads=rheads, dim=128, vdim=128, decay=[1.0 - 2.0 ** (-5 - 3 * i / rheads) for i in range(rheads)],
+    right = dict(heads=rheads, dim=128, vdim=128, decay=[1.0 - 0.05 * 0.5 ** (4 * i / rheads) for i in range(rheads)],
                  rot=dict(dims=128, base=10000.0))
     dense = dict(kind="dense", ff=inter)
     moe = dict(kind="moe", expert=dict(ff=inter // 4 // 8 * 8), router=dict(experts=16, top=4))

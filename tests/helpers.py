@@ -235,9 +235,9 @@ PX_B = dict(architecture="Pemorax", width=50, vocab=77, norm=dict(eps=3e-6), lay
     _px_layer(_px_left(1, 1, 14, 14, conv=1, mask=dict(size=64, keep_first=64)), _px_right(1, 14, 2, [0.96]), dict(kind="dense", ff=45))])
 # C: heads of 64 and of 128 (the sizes tensor-core kernels take), windows longer than several pages, many experts
 PX_C = dict(architecture="Pemorax", width=128, vocab=200, norm=dict(eps=1e-6), layers=[
-    _px_layer(_px_left(4, 2, 64, 64, conv=4, mask=dict(size=70, keep_first=5), rot=dict(dims=64, base=250000.0, scaling=_YARN),
-                       scale=0.125, softcap=30.0),
-              _px_right(2, 64, 64, [0.97, 0.999], rot=dict(dims=64, base=1e6)), _MOE(48, 12, 3)),
+    _px_layer(_px_left(4, 2, 64, 64, conv=4, mask=dict(size=70, keep_first=5), rot=dict(dims=64, base=200000.0, scaling=_YARN),
+                       softcap=30.0),
+              _px_right(2, 64, 64, [0.97, 0.999], rot=dict(dims=64, base=7e5)), _MOE(48, 12, 3)),
     _px_layer(_px_left(2, 1, 128, 128, conv=2, mask=dict(size=100, keep_first=17), rot=dict(dims=64, base=10000.0), softcap=20.0),
               _px_right(1, 128, 128, [0.99], rot=dict(dims=32, base=1e4)), dict(kind="dense", ff=160))])
 PX = {"A": PX_A, "B": PX_B, "C": PX_C}
