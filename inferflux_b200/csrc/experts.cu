@@ -14,7 +14,7 @@
 #include "common.cuh"
 
 namespace {
-constexpr int MAX_TOP = 16;
+constexpr int MAX_TOP = 64;
 
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const float* __restrict__ logits, int n_tokens, int experts, int top,
@@ -41,13 +41,9 @@ moe_route_kernel(const float* __restrict__ logits, int n_tokens, int experts, in
   }
   float sum = 0.0f;
   for (int k = 0; k < top; ++k) sum += expf(vals[k] - vals[0]);      // vals[0] is the largest
-  if (lane < top) {
-    // (a loop, not an index: the arrays stay in registers)
-    for (int k = 0; k < top; ++k)
-      if (k == lane) {
-        chosen[(size_t)t * top + k] = ids[k];
-        weights[(size_t)t * top + k] = expf(vals[k] - vals[0]) / sum;
-      }
+  for (int k = lane; k < top; k += 32) {
+    chosen[(size_t)t * top + k] = ids[k];
+    weights[(size_t)t * top + k] = expf(vals[k] - vals[0]) / sum;
   }
 }
 

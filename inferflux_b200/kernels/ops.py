@@ -1359,7 +1359,7 @@ def moe_route(logits: torch.Tensor, top: int):
     softmax over them alone: (int32 ``[N, top]``, float32 ``[N, top]``)."""
     n, experts = logits.shape
     _need(logits.dtype == torch.float32 and logits.is_contiguous(), "moe_route: float32 logits")
-    _need(1 <= top <= min(16, experts), f"moe_route: top {top} must be within 1..min(16, experts)")
+    _need(1 <= top <= min(64, experts), f"moe_route: top {top} must be within 1..min(64, experts)")
     chosen = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((n, top), dtype=torch.float32, device=logits.device)
     _check(_lib().ifx_moe_route(_ptr(logits), n, experts, top, _ptr(chosen), _ptr(weights), _stream()), "moe_route")

@@ -165,8 +165,8 @@ class RoutedExperts(Part):
         super().__init__(params, prefix, dtype, device)
         self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
         self.experts, self.top = int(params["experts"]), int(params["top"])
-        if not 1 <= self.top <= min(self.experts, 16):
-            raise ValueError(f"routed_experts: top {self.top} must be within 1..min(experts, 16)")
+        if not 1 <= self.top <= min(self.experts, 64):
+            raise ValueError(f"routed_experts: top {self.top} must be within 1..min(experts, 64)")
         self.router: Linear = None
         self.gate_up: torch.Tensor = None
         self.down: torch.Tensor = None

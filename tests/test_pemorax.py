@@ -344,7 +344,8 @@ def test_retention_branch_alone(dtype, name, layer):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hidden,ff,experts,top,rows", [(64, 40, 5, 2, 3), (64, 40, 5, 2, 300), (50, 35, 3, 3, 70), (50, 18, 3, 1, 5),
                                                         (128, 48, 12, 3, 1), (96, 200, 40, 8, 130),
-                                                        (128, 48, 12, 3, 400)])     # bfloat16, 1,200 pairs: the tcgen05 tiles
+                                                        (128, 48, 12, 3, 400),      # bfloat16, 1,200 pairs: the tcgen05 tiles
+                                                        (64, 16, 48, 40, 5)])       # more choices than a warp has lanes
 def test_routed_experts_alone(dtype, hidden, ff, experts, top, rows):
     """Few rows (short tiles) and many (tiles of 64, experts with more than one tile and with none), one expert a
     token and every expert; rows whose choice rests on a close call are left out of the comparison."""
