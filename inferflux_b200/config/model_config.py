@@ -352,7 +352,7 @@ class PemoraxLayer:
 class PemoraxConfig(ModelConfig):
     """``Pemorax``: a decoder whose layers are listed one by one in config.json (``layers``: ``type``, the
     mixer's sizes under ``mixer``, the feed-forward under ``mlp`` or null).  Every sublayer sits between two
-    RMS norms.  The mixer ``parallel`` is two mixers side by side on the same input: ``left`` grouped-query
+    RMS norms.  The mixer ``parallel`` runs a pair of mixers on one input: ``left`` grouped-query
     attention (short convolution on q, k, v, interleaved rotary positions with an optional frequency scaling,
     capped scores, a window that keeps the first tokens, a sink in the softmax, an output gate) and ``right``
     retention (rotate-half positions, a fixed decay per head, a per-head unit norm, a silu gate); their normed

@@ -2,7 +2,7 @@
 // query and key heads, and the write of keys and values into the paged cache, in one kernel:
 //
 //   y_t[c] = sum_{j < taps} w[c][j] * u_{t - taps + 1 + j}[c]        u = the projection's float32 sums,
-//                                                                    zeros before the sequence's start
+//                                                                    u = 0 ahead of a sequence's first token
 //   rotation of the first `rot_dims` dimensions of each query and key head, pairs either interleaved
 //   (2i, 2i+1) or split in halves (i, i + rot_dims/2):  (a, b) -> (a cos - b sin,  b cos + a sin)
 //   with the step's cos/sin tables [token][rot_dims/2];  values are convolved only.

@@ -4,7 +4,7 @@
     o_t = S_t^T q_t
 
 with q and k rotated by the layer's position table (first ``rot_dims`` dimensions, pairs in ``half``s or
-``interleaved``), k then scaled by ``dim^-1/2``; each head's o is divided by its root mean square (no weight),
+``interleaved``), k then scaled by ``dim^-1/2``; each head's o is brought to unit root mean square (no weight),
 the heads side by side are multiplied by silu(g) and projected.  q, k, v and g are one stacked projection whose
 sums stay float32; rotation, state, scores and the norm are float32 in either engine type.  The state lives in
 the request's state slot; portions are cut into segments that run side by side (the recurrence is linear in S).

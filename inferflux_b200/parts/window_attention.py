@@ -3,7 +3,7 @@ decoder designs, each a parameter:
 
   q, k, v (and a gate g) = one stacked projection of the normed input, float32 sums
   ``conv`` taps          a short causal convolution over time on every channel of q, k and v, straight after
-                         the projection: y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros before the sequence
+                         the projection: y_t = sum_j w[:, j] u_(t - taps + 1 + j), with u = 0 ahead of the first token
   rotation               of the first ``rot_dims`` dimensions of every query and key head by the layer's
                          position table, pairs ``interleaved`` (2i, 2i+1) or in ``half``s (i, i + rot_dims/2)
   scores                 s = (q . k) * scale, then ``softcap`` * tanh(s / softcap) if given

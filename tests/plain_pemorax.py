@@ -32,7 +32,7 @@ def silu(z):
 
 def short_conv(u, w, tail=None):
     """y_t = sum_j w[:, j] u_(t - taps + 1 + j) per channel; ``u [T, C]``, ``w [C, taps]``; ``tail`` = the taps-1
-    rows before u (zeros at a sequence's start).  Returns (y, the new tail)."""
+    rows ahead of u (all 0 when u opens a sequence).  Returns (y, the new tail)."""
     taps = w.shape[1]
     if tail is None:
         tail = torch.zeros((taps - 1, u.shape[1]), dtype=u.dtype)
@@ -88,7 +88,7 @@ def visible(n_queries, first_position, mask):
 
 def sink_attention(q, k, v, m, first_position=0):
     """q ``[Tq, H, dim]`` (the last Tq positions), k ``[T, G, dim]``, v ``[T, G, vdim]`` -> ``[Tq, H * vdim]``:
-    scores scaled, capped, masked; softmax with one added to the denominator."""
+    scores scaled, capped, masked; weights exp(s_j) / (1 + sum exp(s))."""
     heads, groups = q.shape[1], k.shape[1]
     see = visible(q.shape[0], first_position, m.get("mask"))
     out = []
